@@ -1,0 +1,467 @@
+/*
+ * CPU oracle for the ring-attention forward path.  TEST INFRASTRUCTURE ONLY.
+ *
+ * Nothing in the shipped library may link, load or call this file; it is the
+ * checker used by the tests, by the smoke check and by the CPU-baseline leg of
+ * the benchmark.
+ *
+ * Parity status: UNPINNED BY THE REFERENCE.  The reference (ykcombat/
+ * RingAttention) ships no golden vectors, no assertions and no CPU attention;
+ * its kernel source is truncated (csrc/ring_attention.cu:244-248) and cannot
+ * be built.  The only executable statement of the math in the reference is
+ * the three PyTorch lines csrc/self_attention.py:22-26
+ *     scores  = Q @ K^T            (:22)
+ *     weights = softmax(scores,-1) (:23)
+ *     output  = weights @ V        (:26)
+ * which this file restates (oracle_attention_fwd / oracle_attention_rows),
+ * and the online-softmax recurrence of csrc/ring_attention.cu:172-245,621-633
+ * which oracle_ring_attention_fwd restates.  The committed fixtures under
+ * tests/golden/ were produced by executing those three reference statements
+ * on CPU tensors (see tests/golden/make_golden.py) and pin the plain path.
+ *
+ * Extensions over the reference, as the benchmark configurations need them:
+ *   - a natural-base softmax scale argument (the reference hard-codes 1.0 and
+ *     feeds it to exp2, csrc/ring_attention.cu:389,597);
+ *   - a causal mask on GLOBAL indices (k_global <= q_global);
+ *   - the per-row log-sum-exp  LSE = ln sum_j exp(scale * q.k_j);
+ *   - batch and heads: tensors are [B, H, S, D] contiguous fp16.
+ *
+ * All tensors are row-major.  fp16 inputs are widened exactly; products and
+ * sums are accumulated in fp32 (accum = 0, "the reference's fp32-accumulated
+ * attention") or fp64 (accum = 1, used as ground truth for tolerances).
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+#define CLONES __attribute__((target_clones("arch=skylake-avx512", "arch=haswell", "default")))
+
+/* ---- fp16 widening (exact) ------------------------------------------------ */
+static float h2f_table[65536];
+static int h2f_ready = 0;
+
+static float h2f_slow(uint16_t h) {
+    uint32_t sign = (uint32_t)(h & 0x8000u) << 16;
+    uint32_t exp = (h >> 10) & 0x1fu;
+    uint32_t man = h & 0x3ffu;
+    uint32_t bits;
+    if (exp == 0) {
+        if (man == 0) {
+            bits = sign;
+        } else { /* subnormal: normalise */
+            int e = -1;
+            do { man <<= 1; e++; } while (!(man & 0x400u));
+            man &= 0x3ffu;
+            bits = sign | ((uint32_t)(127 - 15 - e) << 23) | (man << 13);
+        }
+    } else if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else {
+        bits = sign | ((exp + 127 - 15) << 23) | (man << 13);
+    }
+    float f;
+    memcpy(&f, &bits, 4);
+    return f;
+}
+
+static void h2f_init(void) {
+    if (h2f_ready) return;
+#pragma omp critical(h2f_init_lock)
+    {
+        if (!h2f_ready) {
+            for (uint32_t i = 0; i < 65536u; ++i) h2f_table[i] = h2f_slow((uint16_t)i);
+            h2f_ready = 1;
+        }
+    }
+}
+
+static void widen_f32(const uint16_t* src, float* dst, size_t n) {
+    for (size_t i = 0; i < n; ++i) dst[i] = h2f_table[src[i]];
+}
+
+/* fp32 -> fp16 round-to-nearest-even, used only by the optional "round P like
+ * the GPU does" switch of the blocked variant (csrc/ring_attention.cu:604). */
+static float round_to_f16(float x) {
+    uint32_t b;
+    memcpy(&b, &x, 4);
+    uint32_t sign = b & 0x80000000u;
+    uint32_t a = b & 0x7fffffffu;
+    if (a >= 0x47800000u) { /* >= 65536: overflow to inf (never hit for p <= 256) */
+        uint32_t r = sign | 0x7f800000u;
+        float f; memcpy(&f, &r, 4); return f;
+    }
+    if (a < 0x38800000u) { /* below the fp16 normal range: quantise to 2^-24 */
+        float q = ldexpf(rintf(ldexpf(fabsf(x), 24)), -24);
+        return sign ? -q : q;
+    }
+    uint32_t rem = a & 0x1fffu;
+    a &= ~0x1fffu;
+    if (rem > 0x1000u || (rem == 0x1000u && (a & 0x2000u))) a += 0x2000u;
+    a |= sign;
+    float f; memcpy(&f, &a, 4); return f;
+}
+
+/* ---- dot products ---------------------------------------------------------- */
+CLONES static float dot_f32(const float* a, const float* b, int n) {
+    float acc[16] = {0};
+    int i = 0;
+    for (; i + 16 <= n; i += 16)
+        for (int l = 0; l < 16; ++l) acc[l] += a[i + l] * b[i + l];
+    float s = 0.f;
+    for (int l = 0; l < 16; ++l) s += acc[l];
+    for (; i < n; ++i) s += a[i] * b[i];
+    return s;
+}
+
+CLONES static double dot_f64(const float* a, const float* b, int n) {
+    double acc[8] = {0};
+    int i = 0;
+    for (; i + 8 <= n; i += 8)
+        for (int l = 0; l < 8; ++l) acc[l] += (double)a[i + l] * (double)b[i + l];
+    double s = 0.0;
+    for (int l = 0; l < 8; ++l) s += acc[l];
+    for (; i < n; ++i) s += (double)a[i] * (double)b[i];
+    return s;
+}
+
+CLONES static void axpy_f32(float w, const float* x, float* y, int n) {
+    for (int i = 0; i < n; ++i) y[i] += w * x[i];
+}
+
+CLONES static void axpy_f64(double w, const float* x, double* y, int n) {
+    for (int i = 0; i < n; ++i) y[i] += w * (double)x[i];
+}
+
+/* Number of keys of a shard that row q_global may see. */
+static int64_t visible_keys(int causal, int64_t q_global, int64_t k_off, int64_t Sk) {
+    if (!causal) return Sk;
+    int64_t n = q_global - k_off + 1; /* keys k_off .. q_global */
+    if (n < 0) n = 0;
+    if (n > Sk) n = Sk;
+    return n;
+}
+
+/*
+ * One query row against one (b,h) slab of keys/values, three passes exactly as
+ * csrc/self_attention.py:22-26: scores, softmax over the row, weights @ V.
+ * kf, vf: [Sk, D] fp32 (already widened).  scores: scratch of Sk floats/doubles.
+ */
+static void row_attention_f32(const float* qf, const float* kf, const float* vf, int64_t nvis,
+                              int D, float scale, float* scores, float* o, float* lse) {
+    if (nvis <= 0) {
+        for (int d = 0; d < D; ++d) o[d] = 0.f;
+        *lse = -INFINITY;
+        return;
+    }
+    float mx = -INFINITY;
+    for (int64_t j = 0; j < nvis; ++j) { /* self_attention.py:22 */
+        float s = dot_f32(qf, kf + j * D, D) * scale;
+        scores[j] = s;
+        if (s > mx) mx = s;
+    }
+    float sum = 0.f;
+    for (int64_t j = 0; j < nvis; ++j) { /* self_attention.py:23 */
+        float p = expf(scores[j] - mx);
+        scores[j] = p;
+        sum += p;
+    }
+    float acc[512];
+    for (int d = 0; d < D; ++d) acc[d] = 0.f;
+    for (int64_t j = 0; j < nvis; ++j) axpy_f32(scores[j], vf + j * D, acc, D); /* :26 */
+    float inv = 1.f / sum;
+    for (int d = 0; d < D; ++d) o[d] = acc[d] * inv;
+    *lse = mx + logf(sum);
+}
+
+static void row_attention_f64(const float* qf, const float* kf, const float* vf, int64_t nvis,
+                              int D, double scale, double* scores, float* o, float* lse) {
+    if (nvis <= 0) {
+        for (int d = 0; d < D; ++d) o[d] = 0.f;
+        *lse = -INFINITY;
+        return;
+    }
+    double mx = -INFINITY;
+    for (int64_t j = 0; j < nvis; ++j) {
+        double s = dot_f64(qf, kf + j * D, D) * scale;
+        scores[j] = s;
+        if (s > mx) mx = s;
+    }
+    double sum = 0.0;
+    for (int64_t j = 0; j < nvis; ++j) {
+        double p = exp(scores[j] - mx);
+        scores[j] = p;
+        sum += p;
+    }
+    double acc[512];
+    for (int d = 0; d < D; ++d) acc[d] = 0.0;
+    for (int64_t j = 0; j < nvis; ++j) axpy_f64(scores[j], vf + j * D, acc, D);
+    for (int d = 0; d < D; ++d) o[d] = (float)(acc[d] / sum);
+    *lse = (float)(mx + log(sum));
+}
+
+/*
+ * Full attention of a Q shard against a K/V shard.
+ *   q: [B,H,Sq,D] fp16, k,v: [B,H,Sk,D] fp16, o: [B,H,Sq,D] fp32, lse: [B,H,Sq] fp32.
+ *   q_off / k_off: global sequence index of row 0 of the Q / K shard (causal mask only).
+ *   accum: 0 = fp32, 1 = fp64.
+ * Returns 0, or -1 on bad arguments / allocation failure.
+ */
+int oracle_attention_fwd(const uint16_t* q, const uint16_t* k, const uint16_t* v, int B, int H,
+                         int64_t Sq, int64_t Sk, int D, double scale, int causal, int64_t q_off,
+                         int64_t k_off, int accum, float* o, float* lse) {
+    if (!q || !k || !v || !o || !lse || B <= 0 || H <= 0 || Sq < 0 || Sk < 0 || D <= 0 || D > 512)
+        return -1;
+    h2f_init();
+    int rc = 0;
+    for (int bh = 0; bh < B * H; ++bh) {
+        float* kf = (float*)malloc(sizeof(float) * (size_t)(Sk > 0 ? Sk : 1) * D);
+        float* vf = (float*)malloc(sizeof(float) * (size_t)(Sk > 0 ? Sk : 1) * D);
+        if (!kf || !vf) { free(kf); free(vf); return -1; }
+        widen_f32(k + (size_t)bh * Sk * D, kf, (size_t)Sk * D);
+        widen_f32(v + (size_t)bh * Sk * D, vf, (size_t)Sk * D);
+#pragma omp parallel
+        {
+            void* scores = malloc((accum ? sizeof(double) : sizeof(float)) * (size_t)(Sk > 0 ? Sk : 1));
+            float qf[512];
+            if (!scores) {
+#pragma omp atomic write
+                rc = -1;
+            } else {
+#pragma omp for schedule(dynamic, 8)
+                for (int64_t i = 0; i < Sq; ++i) {
+                    const uint16_t* qi = q + ((size_t)bh * Sq + i) * D;
+                    for (int d = 0; d < D; ++d) qf[d] = h2f_table[qi[d]];
+                    int64_t nvis = visible_keys(causal, q_off + i, k_off, Sk);
+                    float* oi = o + ((size_t)bh * Sq + i) * D;
+                    float* li = lse + (size_t)bh * Sq + i;
+                    if (accum)
+                        row_attention_f64(qf, kf, vf, nvis, D, scale, (double*)scores, oi, li);
+                    else
+                        row_attention_f32(qf, kf, vf, nvis, D, (float)scale, (float*)scores, oi, li);
+                }
+            }
+            free(scores);
+        }
+        free(kf);
+        free(vf);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+/*
+ * Sampled rows in fp64 against the FULL key range of their head: the check used for
+ * sequence lengths whose full attention does not finish on a CPU.
+ *   rows: n triples (b, h, i) with i an index into the Q shard.
+ *   o: [n, D], lse: [n].
+ */
+int oracle_attention_rows(const uint16_t* q, const uint16_t* k, const uint16_t* v, int B, int H,
+                          int64_t Sq, int64_t Sk, int D, double scale, int causal, int64_t q_off,
+                          int64_t k_off, const int64_t* rows, int64_t n, float* o, float* lse) {
+    if (!q || !k || !v || !o || !lse || !rows || D <= 0 || D > 512) return -1;
+    h2f_init();
+    for (int64_t r = 0; r < n; ++r) {
+        if (rows[3 * r] < 0 || rows[3 * r] >= B || rows[3 * r + 1] < 0 || rows[3 * r + 1] >= H ||
+            rows[3 * r + 2] < 0 || rows[3 * r + 2] >= Sq)
+            return -1;
+    }
+    int rc = 0;
+    /* Group by head so each head's K/V is widened once. */
+    for (int bh = 0; bh < B * H; ++bh) {
+        int any = 0;
+        for (int64_t r = 0; r < n; ++r)
+            if (rows[3 * r] * H + rows[3 * r + 1] == bh) { any = 1; break; }
+        if (!any) continue;
+        float* kf = (float*)malloc(sizeof(float) * (size_t)(Sk > 0 ? Sk : 1) * D);
+        float* vf = (float*)malloc(sizeof(float) * (size_t)(Sk > 0 ? Sk : 1) * D);
+        if (!kf || !vf) { free(kf); free(vf); return -1; }
+        widen_f32(k + (size_t)bh * Sk * D, kf, (size_t)Sk * D);
+        widen_f32(v + (size_t)bh * Sk * D, vf, (size_t)Sk * D);
+#pragma omp parallel
+        {
+            double* scores = (double*)malloc(sizeof(double) * (size_t)(Sk > 0 ? Sk : 1));
+            float qf[512];
+            if (!scores) {
+#pragma omp atomic write
+                rc = -1;
+            } else {
+#pragma omp for schedule(dynamic, 1)
+                for (int64_t r = 0; r < n; ++r) {
+                    if (rows[3 * r] * H + rows[3 * r + 1] != bh) continue;
+                    int64_t i = rows[3 * r + 2];
+                    const uint16_t* qi = q + ((size_t)bh * Sq + i) * D;
+                    for (int d = 0; d < D; ++d) qf[d] = h2f_table[qi[d]];
+                    int64_t nvis = visible_keys(causal, q_off + i, k_off, Sk);
+                    row_attention_f64(qf, kf, vf, nvis, D, scale, scores, o + (size_t)r * D, lse + r);
+                }
+            }
+            free(scores);
+        }
+        free(kf);
+        free(vf);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+/*
+ * Cross-step merge of two partial results of the same rows (the standalone form of the
+ * running (max, sum, O) state that csrc/ring_attention.cu:439-443,597-598,621-633 keeps
+ * in registers across ring steps):
+ *   lse' = max + ln(e^{lse_a-max} + e^{lse_b-max}),  O' = e^{lse_a-lse'} O_a + e^{lse_b-lse'} O_b.
+ * A partial with lse = -inf (fully masked) contributes nothing.  In place on (o_a, lse_a).
+ */
+int oracle_lse_merge(float* o_a, float* lse_a, const float* o_b, const float* lse_b, int64_t rows,
+                     int D) {
+    if (!o_a || !lse_a || !o_b || !lse_b || D <= 0) return -1;
+#pragma omp parallel for schedule(static)
+    for (int64_t r = 0; r < rows; ++r) {
+        double la = lse_a[r], lb = lse_b[r];
+        double mx = la > lb ? la : lb;
+        if (mx == -INFINITY) { /* both empty */
+            for (int d = 0; d < D; ++d) o_a[r * D + d] = 0.f;
+            lse_a[r] = -INFINITY;
+            continue;
+        }
+        double ea = exp(la - mx), eb = exp(lb - mx);
+        double tot = ea + eb;
+        double wa = ea / tot, wb = eb / tot;
+        for (int d = 0; d < D; ++d)
+            o_a[r * D + d] = (float)(wa * (double)o_a[r * D + d] + wb * (double)o_b[r * D + d]);
+        lse_a[r] = (float)(mx + log(tot));
+    }
+    return 0;
+}
+
+/*
+ * Blocked ring attention, restating the device algorithm of the reference:
+ *   - P ranks, contiguous even shards of S rows (csrc/ring.h:9 seqlen[], equal here);
+ *   - rank r visits source ranks (r + step) % P in that order (csrc/ring_attention.cu:463,531);
+ *   - inside a source shard, key blocks of block_n rows (csrc/ring_attention.cu:536);
+ *   - online softmax in the exp2 form with the -inf guard (csrc/ring_attention.cu:172-192):
+ *       m' = max(m, rowmax(S)); alpha = exp2((m - m') c); l = l alpha + rowsum(p);
+ *       O = O alpha + p V;  p = exp2(S c - m' c), c = scale * log2(e)
+ *     (csrc/ring_attention.cu:194-245; the truncated tail is  l += l_cur);
+ *   - final O /= l with the l == 0 guard (csrc/ring_attention.cu:621-633).
+ * Arithmetic is fp32 like the device code.  round_p != 0 rounds p to fp16 before the PV
+ * product, as csrc/ring_attention.cu:604 does, while the row sum keeps the unrounded p (:242).
+ *   q,k,v: [B,H,S,D] fp16 (all ranks' shards concatenated along S), o: [B,H,S,D], lse: [B,H,S].
+ * Causal: a source shard strictly after the Q shard is skipped; the diagonal shard masks
+ * k_global > q_global.
+ */
+int oracle_ring_attention_fwd(const uint16_t* q, const uint16_t* k, const uint16_t* v, int B, int H,
+                              int64_t S, int D, int P, int block_n, double scale, int causal,
+                              int round_p, float* o, float* lse) {
+    if (!q || !k || !v || !o || !lse || P <= 0 || S % P != 0 || block_n <= 0 || D <= 0 || D > 512)
+        return -1;
+    h2f_init();
+    const int64_t Sl = S / P;
+    const float c = (float)(scale * 1.4426950408889634074);
+    int rc = 0;
+    for (int bh = 0; bh < B * H; ++bh) {
+        float* kf = (float*)malloc(sizeof(float) * (size_t)S * D);
+        float* vf = (float*)malloc(sizeof(float) * (size_t)S * D);
+        if (!kf || !vf) { free(kf); free(vf); return -1; }
+        widen_f32(k + (size_t)bh * S * D, kf, (size_t)S * D);
+        widen_f32(v + (size_t)bh * S * D, vf, (size_t)S * D);
+#pragma omp parallel
+        {
+            float* s = (float*)malloc(sizeof(float) * (size_t)block_n);
+            float qf[512], acc[512];
+            if (!s) {
+#pragma omp atomic write
+                rc = -1;
+            } else {
+#pragma omp for schedule(dynamic, 8)
+                for (int64_t gi = 0; gi < S; ++gi) {
+                    const int r = (int)(gi / Sl);
+                    const uint16_t* qi = q + ((size_t)bh * S + gi) * D;
+                    for (int d = 0; d < D; ++d) { qf[d] = h2f_table[qi[d]]; acc[d] = 0.f; }
+                    float m = -INFINITY, l = 0.f;
+                    for (int step = 0; step < P; ++step) {
+                        const int src = (r + step) % P;
+                        if (causal && src > r) continue;
+                        const int64_t k0 = (int64_t)src * Sl;
+                        const int64_t nvis = visible_keys(causal, gi, k0, Sl);
+                        for (int64_t jb = 0; jb < nvis; jb += block_n) {
+                            const int nb = (int)((nvis - jb) < block_n ? (nvis - jb) : block_n);
+                            float bm = -INFINITY;
+                            for (int j = 0; j < nb; ++j) {
+                                s[j] = dot_f32(qf, kf + (size_t)(k0 + jb + j) * D, D);
+                                if (s[j] > bm) bm = s[j];
+                            }
+                            const float m_new = bm > m ? bm : m;
+                            const float m_scaled = (m_new == -INFINITY) ? 0.f : m_new * c;
+                            const float alpha = (m == -INFINITY) ? 0.f : exp2f((m - m_new) * c);
+                            l *= alpha;
+                            for (int d = 0; d < D; ++d) acc[d] *= alpha;
+                            float l_cur = 0.f;
+                            for (int j = 0; j < nb; ++j) {
+                                float p = exp2f(s[j] * c - m_scaled);
+                                l_cur += p;
+                                if (round_p) p = round_to_f16(p);
+                                axpy_f32(p, vf + (size_t)(k0 + jb + j) * D, acc, D);
+                            }
+                            l += l_cur;
+                            m = m_new;
+                        }
+                    }
+                    float* oi = o + ((size_t)bh * S + gi) * D;
+                    const float inv = (l == 0.f || l != l) ? 1.f : 1.f / l;
+                    for (int d = 0; d < D; ++d) oi[d] = acc[d] * inv;
+                    lse[(size_t)bh * S + gi] =
+                        (l == 0.f) ? -INFINITY : (float)(m * scale) + logf(l);
+                }
+            }
+            free(s);
+        }
+        free(kf);
+        free(vf);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+/*
+ * The deterministic fill of the reference's driver, csrc/ring_attention.cu:731-741:
+ *   h[i][j] = i/130 + j/110 + i*j/600, computed in double and rounded to fp16
+ * (the reference assigns a double to cute::half_t).  dst: [m, n] fp16 bit patterns.
+ */
+static uint16_t f2h_rn(double x) {
+    float f = (float)x;
+    /* double -> float -> half double-rounds in rare ties; the reference's half_t(double)
+     * goes through float as well (cutlass::half_t has a float constructor). */
+    float r = round_to_f16(f);
+    uint32_t b;
+    memcpy(&b, &r, 4);
+    uint32_t sign = (b >> 16) & 0x8000u;
+    uint32_t a = b & 0x7fffffffu;
+    if (a >= 0x7f800000u) return (uint16_t)(sign | 0x7c00u);
+    if (a == 0) return (uint16_t)sign;
+    int32_t e = (int32_t)(a >> 23) - 127 + 15;
+    if (e <= 0) { /* subnormal half: value is a multiple of 2^-24 */
+        float mag = fabsf(r);
+        return (uint16_t)(sign | (uint32_t)lrintf(ldexpf(mag, 24)));
+    }
+    return (uint16_t)(sign | ((uint32_t)e << 10) | ((a >> 13) & 0x3ffu));
+}
+
+int oracle_fill_with_num(uint16_t* dst, int64_t m, int64_t n) {
+    if (!dst) return -1;
+    for (int64_t i = 0; i < m; ++i)
+        for (int64_t j = 0; j < n; ++j)
+            dst[i * n + j] = f2h_rn((double)i / 130.0 + (double)j / 110.0 + (double)(i * j) / 600.0);
+    return 0;
+}
+
+int oracle_num_threads(void) {
+#ifdef _OPENMP
+    return omp_get_max_threads();
+#else
+    return 1;
+#endif
+}
