@@ -1,0 +1,149 @@
+/*
+ * C ABI of the B200 ring-attention forward.  Plain pointers and sizes only; no torch, CUDA C++ or
+ * CuTe types cross this boundary (cudaStream_t and ncclUniqueId travel as void* / byte arrays).
+ *
+ * Each entry point cites the interface of ykcombat/RingAttention it stands in for.  The reference
+ * exports no C symbols at all: its include/attention_api.cuh holds macros only and its operator
+ * boundary is the C++ function ring_attention() at csrc/ring_attention.cu:706.
+ *
+ * Conventions
+ *   - every function returns 0 on success or a negative RingStatus; nothing calls exit()
+ *     (the reference prints and exits, csrc/utils.h:1-11);
+ *   - device tensors are contiguous: Q, K, V  [batch, heads, seqlen_local, dim] fp16 (or bf16),
+ *     O [batch, heads, seqlen_local, dim] fp32, LSE [batch, heads, seqlen_local] fp32 (natural log);
+ *     per (batch, head) this is the reference's [seqlen, dim] row-major matrix
+ *     (csrc/ring_attention.cu:422-454); all base pointers 16-byte aligned;
+ *   - dim is 64 or 128; seqlen_local is a multiple of 128 and equal on all ranks;
+ *   - one process per GPU; a context belongs to the device that was current when it was created.
+ */
+#ifndef RING_ATTENTION_B200_H_
+#define RING_ATTENTION_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum RingStatus {
+    RING_OK = 0,
+    RING_ERR_INVALID_ARGUMENT = -1, /* null pointer, dim not in {64,128}, seqlen % 128 != 0, uneven shards ... */
+    RING_ERR_CUDA = -2,             /* a CUDA runtime/driver call failed; see ring_last_error_string() */
+    RING_ERR_NCCL = -3,             /* an NCCL call failed or NCCL could not be loaded */
+    RING_ERR_DEVICE_TIMEOUT = -4,   /* a bounded wait inside a kernel ran out; the device status word says which */
+    RING_ERR_NO_CONTEXT = -5,       /* ring_attention() with npes > 1 before ring_set_default_ctx() */
+    RING_ERR_UNSUPPORTED = -6
+} RingStatus;
+
+#define RING_UNIQUE_ID_BYTES 128
+
+typedef struct RingCtx RingCtx; /* opaque: communicator, side stream, events, receive buffers, workspace */
+
+struct Ring_fwd_params; /* csrc/ring.h of this repository: the reference's struct (csrc/ring.h:5-19) plus extensions */
+
+/* How the cross-step merge runs (ring_ctx_set_option(ctx, RING_OPT_MERGE_MODE, v)). */
+#define RING_MERGE_SEPARATE_KERNEL 0 /* block kernel writes a partial, ring_lse_merge folds it in */
+#define RING_MERGE_FUSED_EPILOGUE 1  /* block kernel folds its tile into the running result itself */
+
+#define RING_OPT_MERGE_MODE 1
+#define RING_OPT_CAUSAL_SKIP_EXCHANGE 2 /* 1 (default): under a causal mask, do not ship shards nobody will read */
+#define RING_OPT_RECORD_TIMINGS 3       /* 1: record per-step events so ring_ctx_get_timings() works */
+
+/*
+ * Replaces: ring_attention(FPC* q, FPC* k, FPC* v, float* out, int npes, int mype, int* seqlen,
+ *                          int dim, int max_seq)                    -- csrc/ring_attention.cu:706-722
+ * Same argument order and meaning: single batch, single head, q/k/v [seqlen[mype], dim] fp16 device
+ * pointers, out [seqlen[mype], dim] fp32 device pointer, seqlen a HOST array of npes entries
+ * (all equal), max_seq an upper bound on them.  Non-causal.  Synchronous like the reference
+ * (which ends in cudaDeviceSynchronize, :721).  The softmax scale is 1/sqrt(dim) in the natural
+ * base (the reference's kernel applies exp2 with scale 1, csrc/ring_attention.cu:389,597, which
+ * disagrees with its own PyTorch check csrc/self_attention.py:22-26; see ring_attention_scaled).
+ * With npes > 1 the exchange runs over the context registered by ring_set_default_ctx().
+ */
+int ring_attention(const void* q, const void* k, const void* v, float* out, int npes, int mype,
+                   const int* seqlen, int dim, int max_seq);
+
+/* Same call with an explicit natural-base softmax scale (1.0 gives csrc/self_attention.py:22-26). */
+int ring_attention_scaled(const void* q, const void* k, const void* v, float* out, int npes, int mype,
+                          const int* seqlen, int dim, int max_seq, float softmax_scale);
+
+/*
+ * Replaces: nvshmem_init / nvshmem_my_pe / nvshmem_n_pes and the symmetric allocations of
+ * csrc/ring_attention.cu:754-761 and :391-393 (k_buffer / v_buffer allocated per call and leaked).
+ * ring_get_unique_id: rank 0 obtains RING_UNIQUE_ID_BYTES bytes and hands them to the other ranks by any
+ * host channel.  ring_ctx_create: collective over `world` processes; owns the NCCL communicator, the
+ * exchange stream, events and (grown on demand, never per call in steady state) the two receive
+ * buffers and the partial-result workspace.  world == 1 needs no id (pass NULL) and no NCCL.
+ */
+int ring_get_unique_id(void* id_out);
+int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id);
+int ring_ctx_destroy(RingCtx* ctx);
+int ring_ctx_set_option(RingCtx* ctx, int option, int value);
+int ring_set_default_ctx(RingCtx* ctx); /* context used by ring_attention(); NULL clears it */
+
+/*
+ * Single-process stand-in for the multi-process launch of the reference (`nvshmrun -n 2`, makefile:2):
+ * `world` virtual ranks share one GPU and the exchange is a device-to-device copy on the exchange
+ * stream.  The caller registers every virtual rank's K and V shard, then calls ring_attention_fwd()
+ * once per virtual rank (params.mype selects it).  Used to test the ring schedule on one GPU.
+ */
+int ring_ctx_create_local(RingCtx** ctx, int world);
+int ring_ctx_set_local_shards(RingCtx* ctx, const void* const* k_shards, const void* const* v_shards);
+
+/*
+ * Replaces: set_params_fprop + run_ring_fwd<Traits> (csrc/ring_attention.cu:361-395, 669-704), i.e. the
+ * whole ring loop of ring_attention_kernel (:456-619) with batch, heads, causal mask and LSE output.
+ * Asynchronous on params->stream.  Step i attends to the shard of rank (mype + i) % npes
+ * (csrc/ring_attention.cu:463); while it computes, the shard for step i + 1 arrives on the exchange stream.
+ */
+int ring_attention_fwd(RingCtx* ctx, const struct Ring_fwd_params* params);
+
+/* Blocks until everything the context has enqueued is done and returns the device status
+ * (RING_OK or RING_ERR_DEVICE_TIMEOUT / RING_ERR_CUDA). */
+int ring_ctx_synchronize(RingCtx* ctx);
+
+/*
+ * Per-step timings of the last ring_attention_fwd() (needs RING_OPT_RECORD_TIMINGS = 1 and a prior
+ * ring_ctx_synchronize()).  Arrays of `n` >= npes floats, milliseconds:
+ *   compute_ms[i]  block kernel (+ merge) of step i;   comm_ms[i]  exchange posted during step i;
+ *   exposed_ms[i]  time step i + 1 had to wait for that exchange after step i's compute was done.
+ * Stands in for the cudaEvent timing of the reference driver (csrc/ring_attention.cu:773-783).
+ */
+int ring_ctx_get_timings(RingCtx* ctx, float* compute_ms, float* comm_ms, float* exposed_ms, int n);
+
+/*
+ * Replaces: one pass of the flash inner loop of ring_attention_kernel over ONE source shard
+ * (csrc/ring_attention.cu:536-609) plus the final normalisation (:621-664).
+ * q [B,H,Sq,D], k/v [B,H,Sk,D] -> o [B,H,Sq,D] fp32, lse [B,H,Sq] fp32.  q_off / k_off are the global
+ * sequence indices of row 0 of each shard (causal mask: k_off + j <= q_off + i).
+ * merge = 0 overwrites o / lse; merge = 1 folds the result into the partial they already hold.
+ * Asynchronous on `stream` (a cudaStream_t passed as void*; NULL = default stream).
+ */
+int ring_attention_block_fwd(const void* q, const void* k, const void* v, float* o, float* lse, int batch,
+                             int heads, int sq, int sk, int dim, float softmax_scale, int causal,
+                             int64_t q_off, int64_t k_off, int merge, int is_bf16, void* stream);
+
+/*
+ * Replaces: the implicit cross-step accumulation of csrc/ring_attention.cu:439-443, 597-598, 621-633
+ * (running max / sum / O kept in registers across PEs) as a standalone pass over memory:
+ * (o_acc, lse_acc) <- merge((o_acc, lse_acc), (o_part, lse_part)) for `rows` rows of `dim` floats.
+ */
+int ring_lse_merge(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part, int64_t rows,
+                   int dim, void* stream);
+
+/* Device status word of the current device: 0, or the code of the bounded wait that ran out
+ * (1xx, see csrc/block_attention.cuh).  ring_device_status synchronises the device. */
+int ring_device_status(int* status_out);
+int ring_device_status_reset(void);
+
+/* Number of kernels this library has launched in this process (block + merge), for accounting. */
+int64_t ring_kernel_launch_count(void);
+
+/* Thread-local description of the last error returned to this thread. */
+const char* ring_last_error_string(void);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* RING_ATTENTION_B200_H_ */

@@ -1,0 +1,73 @@
+// Compile-time shape configuration of the block-attention kernel.
+//
+// Same template signature and constant names as the reference's Ring_kernel_traits /
+// Ring_fwd_traits<kHeadDim, kBlockM, kBlockN, kNWarps, elem> (csrc/kernel_traits.h:11-44, 47-177):
+// kNWarps, kNThreads, kBlockM, kBlockN, kHeadDim, kSmemSize, Element, ElementAccum, index_t.
+// The contents are sm_100a: TMA boxes with the 128-byte swizzle instead of cp.async tiled copies,
+// tcgen05 UMMA shapes instead of the mma.sync TiledMma, a TMEM column budget, a K/V stage ring and
+// warp roles.  No CuTe types.
+#pragma once
+
+#include <cstdint>
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <type_traits>
+
+template <int kHeadDim_, int kBlockM_, int kBlockN_, int kNWarps_, typename elem_type = __half>
+struct Ring_kernel_traits
+{
+    using Element = elem_type;
+    using ElementAccum = float;
+    using index_t = int64_t;
+    static constexpr bool kIsBf16 = std::is_same<elem_type, __nv_bfloat16>::value;
+
+    // UMMA instruction shape (cta_group::1): M x N x 16 for 16-bit operands.
+    static constexpr int kUmmaM = 128;
+    static constexpr int kUmmaK = 16;
+    // One TMA box / one swizzle row = 64 elements = 128 bytes.
+    static constexpr int kSwizzleElems = 64;
+    static constexpr int kSwizzleAtomBytes = 1024;  // 8 rows x 128 B
+};
+
+template <int kHeadDim_, int kBlockM_, int kBlockN_, int kNWarps_, typename elem_type = __half,
+          typename Base = Ring_kernel_traits<kHeadDim_, kBlockM_, kBlockN_, kNWarps_, elem_type>>
+struct Ring_fwd_traits : public Base
+{
+    using Element = typename Base::Element;
+    using ElementAccum = typename Base::ElementAccum;
+    using index_t = typename Base::index_t;
+
+    static constexpr int kNWarps = kNWarps_;
+    static constexpr int kNThreads = kNWarps * 32;
+
+    static constexpr int kBlockM = kBlockM_;  // Q rows per CTA = kQTiles x 128
+    static constexpr int kBlockN = kBlockN_;  // K/V rows per pipeline stage
+    static constexpr int kHeadDim = kHeadDim_;
+
+    static_assert(kHeadDim == 64 || kHeadDim == 128, "head dimension must be 64 or 128");
+    static_assert(kBlockM == 256, "a CTA owns two 128-row Q tiles");
+    static_assert(kBlockN == 128, "K/V blocks are 128 rows");
+
+    // ---- warp roles -----------------------------------------------------------------------
+    static constexpr int kQTiles = kBlockM / Base::kUmmaM;       // 2: ping-pong pair
+    static constexpr int kSoftmaxWarps = 4 * kQTiles;            // one warpgroup per Q tile, 1 thread = 1 row
+    static constexpr int kMmaWarp = kSoftmaxWarps;               // single-thread UMMA issue
+    static constexpr int kLoadWarp = kSoftmaxWarps + 1;          // single-thread TMA issue
+    static_assert(kNWarps == kSoftmaxWarps + 2, "8 softmax warps + MMA warp + load warp");
+
+    // ---- shared memory ----------------------------------------------------------------------
+    static constexpr int kBoxesPerTile = kHeadDim / Base::kSwizzleElems;       // TMA boxes per 128-row tile
+    static constexpr int kBoxBytes = 128 * Base::kSwizzleElems * 2;            // 16 KiB
+    static constexpr int kTileBytes = kBoxesPerTile * kBoxBytes;               // one 128 x kHeadDim tile
+    static constexpr int kStages = kHeadDim == 128 ? 5 : 8;                    // K/V ring slots (K and V alternate)
+    static constexpr int kNumBarriers = 2 /*q_full*/ + 2 * kStages + 3 * kQTiles /*s_full,p_full,o_done*/;
+    static constexpr int kSmemTiles = (kQTiles + kStages) * kTileBytes;
+    static constexpr int kSmemSize = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers, TMEM slot, flags*/;
+    static_assert(kSmemSize <= 227 * 1024, "exceeds the 227 KiB per-CTA limit");
+
+    // ---- tensor memory (512 columns x 128 lanes x 32 bit) ------------------------------------------
+    static constexpr int kTmemCols = 512;
+    static constexpr int kTmemS0 = 0;                 // S tile t at columns t*128; fp16 P aliases its first 64
+    static constexpr int kTmemO0 = kQTiles * kBlockN; // O tile t at kTmemO0 + t*kHeadDim
+    static_assert(kTmemO0 + kQTiles * kHeadDim <= kTmemCols, "TMEM budget");
+};

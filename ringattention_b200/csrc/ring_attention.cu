@@ -1,0 +1,748 @@
+// Host side of the B200 ring-attention forward: launchers, the ring driver loop, the K/V exchange
+// and the C ABI.
+//
+// Keeps the reference's three host entry points by name and role:
+//   set_params_fprop  (csrc/ring_attention.cu:361-395)  fill Ring_fwd_params
+//   run_ring_fwd<Kernel_traits>  (csrc/ring_attention.cu:669-704)  derive grid / shared memory and launch
+//   ring_attention  (csrc/ring_attention.cu:706-722)  the call users make
+// with these differences: nothing is allocated per call (the reference allocates d_seqlen, k_buffer and
+// v_buffer on every call and never frees them, :384,391,393); run_ring_fwd is the ring loop itself
+// (one block-kernel launch per ring step instead of one kernel looping over PEs, :456) and honours its
+// stream argument (the reference launches on stream 0, :700); the exchange is NCCL send/recv on a side
+// stream into two alternating receive buffers instead of an in-kernel NVSHMEM get into a single buffer
+// (:611-619); errors are returned, not printed-and-exit (csrc/utils.h:1-11).
+#include <atomic>
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <dlfcn.h>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <nccl.h>
+
+#include "../../include/ring_attention_b200.h"
+#include "block_attention.cuh"
+#include "kernel_traits.h"
+#include "lse_merge.cuh"
+#include "ring.h"
+
+namespace {
+
+// ------------------------------------------------------------------------------------------ errors
+thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define RING_CUDA(call)                                                                              \
+    do {                                                                                             \
+        cudaError_t e_ = (call);                                                                     \
+        if (e_ != cudaSuccess)                                                                       \
+            return fail(RING_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, \
+                        __LINE__);                                                                   \
+    } while (0)
+
+std::atomic<int64_t> g_launches{0};
+
+// ------------------------------------------------------------------------------------------ NCCL (loaded lazily)
+// The library is usable on one GPU without NCCL being present; multi-rank contexts load it on demand.
+// Inside a process that already loaded a libnccl.so.2 (for example through torch) the same copy is used.
+struct NcclApi {
+    void* handle = nullptr;
+    ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+    ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*GroupStart)() = nullptr;
+    ncclResult_t (*GroupEnd)() = nullptr;
+    const char* (*GetErrorString)(ncclResult_t) = nullptr;
+    ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t*) = nullptr;
+    bool ok = false;
+};
+
+NcclApi& nccl() {
+    static NcclApi api;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        const char* names[] = {"libnccl.so.2", "libnccl.so"};
+        for (const char* n : names) {
+            api.handle = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+            if (api.handle) break;
+        }
+        if (!api.handle) return;
+#define LOAD(field, sym)                                                     \
+    api.field = reinterpret_cast<decltype(api.field)>(dlsym(api.handle, sym)); \
+    if (!api.field) return;
+        LOAD(GetUniqueId, "ncclGetUniqueId");
+        LOAD(CommInitRank, "ncclCommInitRank");
+        LOAD(CommDestroy, "ncclCommDestroy");
+        LOAD(CommAbort, "ncclCommAbort");
+        LOAD(Send, "ncclSend");
+        LOAD(Recv, "ncclRecv");
+        LOAD(GroupStart, "ncclGroupStart");
+        LOAD(GroupEnd, "ncclGroupEnd");
+        LOAD(GetErrorString, "ncclGetErrorString");
+        LOAD(CommGetAsyncError, "ncclCommGetAsyncError");
+#undef LOAD
+        api.ok = true;
+    });
+    return api;
+}
+
+#define RING_NCCL(call)                                                                                \
+    do {                                                                                               \
+        ncclResult_t r_ = (call);                                                                      \
+        if (r_ != ncclSuccess)                                                                         \
+            return fail(RING_ERR_NCCL, "%s failed: %s (%s:%d)", #call, nccl().GetErrorString(r_), __FILE__, \
+                        __LINE__);                                                                     \
+    } while (0)
+
+// ------------------------------------------------------------------------------------------ per-device state
+struct DeviceState {
+    int* d_status = nullptr;  // device status word written by kernels whose bounded waits ran out
+    bool attr_set[2][2] = {{false, false}, {false, false}};  // [dim==128][bf16]
+};
+
+std::mutex g_dev_mutex;
+DeviceState g_dev[64];
+
+int device_state(DeviceState** out) {
+    int dev = 0;
+    RING_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RING_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.d_status) {
+        RING_CUDA(cudaMalloc(&st.d_status, sizeof(int)));
+        RING_CUDA(cudaMemset(st.d_status, 0, sizeof(int)));
+    }
+    *out = &st;
+    return RING_OK;
+}
+
+// ------------------------------------------------------------------------------------------ tensor maps
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_fn(EncodeTiledFn* out) {
+    static EncodeTiledFn fn = nullptr;
+    static std::mutex m;
+    std::lock_guard<std::mutex> lock(m);
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        RING_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !p)
+            return fail(RING_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    *out = fn;
+    return RING_OK;
+}
+
+// [batch, heads, rows, dim] 16-bit tensor -> 4-D map, box = 64 x 128 x 1 x 1 elements, 128-byte swizzle.
+// Out-of-range rows read as zero, which gives tail predication for free (the reference has none and
+// needs seqlen % 64 == 0, csrc/ring_attention.cu:131,143-145).
+int make_tensor_map(CUtensorMap* tm, const void* base, int batch, int heads, int rows, int dim, bool bf16) {
+    EncodeTiledFn enc = nullptr;
+    int rc = encode_fn(&enc);
+    if (rc) return rc;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(rows),
+                                static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(rows) * dim * 2,
+                                   static_cast<cuuint64_t>(heads) * rows * dim * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(RING_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return RING_OK;
+}
+
+// ------------------------------------------------------------------------------------------ launchers
+struct BlockLaunch {
+    const void *q, *k, *v;
+    float* o;
+    float* lse;
+    int batch, heads, sq, sk, dim;
+    float scale;
+    int causal;
+    int64_t q_off, k_off;
+    int merge;
+    int is_bf16;
+};
+
+template <class Traits>
+int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t stream) {
+    auto kernel = &ring::ring_block_attention_kernel<Traits>;
+    bool& attr = st->attr_set[Traits::kHeadDim == 128][Traits::kIsBf16];
+    if (!attr) {
+        RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
+        attr = true;
+    }
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map(&tq, L.q, L.batch, L.heads, L.sq, L.dim, L.is_bf16))) return rc;
+    if ((rc = make_tensor_map(&tk, L.k, L.batch, L.heads, L.sk, L.dim, L.is_bf16))) return rc;
+    if ((rc = make_tensor_map(&tv, L.v, L.batch, L.heads, L.sk, L.dim, L.is_bf16))) return rc;
+
+    ring::BlockFwdArgs a;
+    a.o = L.o;
+    a.lse = L.lse;
+    a.o_row_stride = L.dim;
+    a.o_head_stride = static_cast<int64_t>(L.sq) * L.dim;
+    a.o_batch_stride = a.o_head_stride * L.heads;
+    a.lse_head_stride = L.sq;
+    a.lse_batch_stride = static_cast<int64_t>(L.sq) * L.heads;
+    a.heads = L.heads;
+    a.sq = L.sq;
+    a.sk = L.sk;
+    a.scale = L.scale;
+    a.scale_log2 = L.scale * 1.4426950408889634f;
+    a.causal = L.causal ? 1 : 0;
+    int64_t diag = L.q_off - L.k_off;
+    const int64_t lim = int64_t(1) << 30;
+    diag = diag > lim ? lim : (diag < -lim ? -lim : diag);
+    a.diag = static_cast<int>(diag);
+    a.merge = L.merge ? 1 : 0;
+    a.status = st->d_status;
+
+    dim3 grid((L.sq + Traits::kBlockM - 1) / Traits::kBlockM, L.batch * L.heads);
+    dim3 block(Traits::kNThreads);
+    kernel<<<grid, block, Traits::kSmemSize, stream>>>(tq, tk, tv, a);
+    RING_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RING_OK;
+}
+
+int validate_block(const BlockLaunch& L) {
+    if (!L.q || !L.k || !L.v || !L.o || !L.lse) return fail(RING_ERR_INVALID_ARGUMENT, "null tensor pointer");
+    if (L.dim != 64 && L.dim != 128) return fail(RING_ERR_INVALID_ARGUMENT, "dim must be 64 or 128, got %d", L.dim);
+    if (L.batch <= 0 || L.heads <= 0 || L.sq <= 0 || L.sk <= 0)
+        return fail(RING_ERR_INVALID_ARGUMENT, "batch, heads and sequence lengths must be positive");
+    if (L.sq % 128 != 0 || L.sk % 128 != 0)
+        return fail(RING_ERR_INVALID_ARGUMENT, "sequence lengths must be multiples of 128 (got %d, %d)", L.sq, L.sk);
+    if (static_cast<int64_t>(L.batch) * L.heads > 65535)
+        return fail(RING_ERR_INVALID_ARGUMENT, "batch * heads must not exceed 65535");
+    if (!(L.scale > 0.f) || !std::isfinite(L.scale))
+        return fail(RING_ERR_INVALID_ARGUMENT, "softmax_scale must be positive and finite");
+    const uintptr_t al = reinterpret_cast<uintptr_t>(L.q) | reinterpret_cast<uintptr_t>(L.k) |
+                         reinterpret_cast<uintptr_t>(L.v) | reinterpret_cast<uintptr_t>(L.o);
+    if (al & 15) return fail(RING_ERR_INVALID_ARGUMENT, "tensor base pointers must be 16-byte aligned");
+    return RING_OK;
+}
+
+// Shape dispatch: the reference instantiates Ring_fwd_traits<64, 64, 64, 4, half> only
+// (csrc/ring_attention.cu:707-716); here <64|128, 256, 128, 10, half|bf16>.
+int launch_block(const BlockLaunch& L, cudaStream_t stream) {
+    int rc = validate_block(L);
+    if (rc) return rc;
+    DeviceState* st = nullptr;
+    if ((rc = device_state(&st))) return rc;
+    if (L.dim == 128) {
+        if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 10, __nv_bfloat16>>(L, st, stream);
+        return launch_block_instance<Ring_fwd_traits<128, 256, 128, 10, __half>>(L, st, stream);
+    }
+    if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<64, 256, 128, 10, __nv_bfloat16>>(L, st, stream);
+    return launch_block_instance<Ring_fwd_traits<64, 256, 128, 10, __half>>(L, st, stream);
+}
+
+int launch_merge(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part, int64_t rows, int dim,
+                 cudaStream_t stream) {
+    if (!o_acc || !lse_acc || !o_part || !lse_part) return fail(RING_ERR_INVALID_ARGUMENT, "null tensor pointer");
+    if (dim != 64 && dim != 128) return fail(RING_ERR_INVALID_ARGUMENT, "dim must be 64 or 128, got %d", dim);
+    if (rows < 0) return fail(RING_ERR_INVALID_ARGUMENT, "negative row count");
+    if (rows == 0) return RING_OK;
+    int dev = 0, sms = 148;
+    RING_CUDA(cudaGetDevice(&dev));
+    RING_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    const int threads = 256;
+    const int64_t want = (rows + 7) / 8;              // 8 warps (rows) per block
+    const int64_t cap = static_cast<int64_t>(sms) * 8;  // 8 resident blocks per SM, grid-stride beyond that
+    const int blocks = static_cast<int>(want < cap ? want : cap);
+    if (dim == 128)
+        ring::ring_lse_merge_kernel<128><<<blocks, threads, 0, stream>>>(o_acc, lse_acc, o_part, lse_part, rows);
+    else
+        ring::ring_lse_merge_kernel<64><<<blocks, threads, 0, stream>>>(o_acc, lse_acc, o_part, lse_part, rows);
+    RING_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RING_OK;
+}
+
+int read_status(int* out) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    RING_CUDA(cudaDeviceSynchronize());
+    RING_CUDA(cudaMemcpy(out, st->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    return RING_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ context
+constexpr int kMaxWorld = 64;
+
+struct RingCtx {
+    int rank = 0;
+    int world = 1;
+    int device = 0;
+    bool local = false;  // virtual ranks on one GPU, exchange by device-to-device copy
+    ncclComm_t comm = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t ev_fork = nullptr;
+    cudaEvent_t ev_recv_done[kMaxWorld] = {};
+    cudaEvent_t ev_comm_start[kMaxWorld] = {};
+    cudaEvent_t ev_compute_start[kMaxWorld] = {};
+    cudaEvent_t ev_compute_done[kMaxWorld] = {};
+    // receive double buffer: recv[i] holds K then V of one shard
+    void* recv[2] = {nullptr, nullptr};
+    size_t recv_cap[2] = {0, 0};  // bytes
+    // partial result of one step (separate-kernel merge mode) and an LSE buffer for callers that pass none
+    float* o_part = nullptr;
+    float* lse_part = nullptr;
+    float* lse_own = nullptr;
+    size_t o_part_cap = 0, lse_part_cap = 0, lse_own_cap = 0;  // bytes
+    int merge_mode = RING_MERGE_FUSED_EPILOGUE;
+    int causal_skip = 1;
+    int record_timings = 0;
+    int last_steps = 0;
+    bool step_computed[kMaxWorld] = {};
+    bool step_exchanged[kMaxWorld] = {};
+    const void* local_k[kMaxWorld] = {};
+    const void* local_v[kMaxWorld] = {};
+};
+
+namespace {
+
+RingCtx* g_default_ctx = nullptr;
+RingCtx* g_solo_ctx = nullptr;  // world-1 context created on demand by ring_attention()
+
+int ctx_common_init(RingCtx* c) {
+    RING_CUDA(cudaGetDevice(&c->device));
+    RING_CUDA(cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking));
+    RING_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    for (int i = 0; i < c->world; ++i) {
+        RING_CUDA(cudaEventCreate(&c->ev_recv_done[i]));
+        RING_CUDA(cudaEventCreate(&c->ev_comm_start[i]));
+        RING_CUDA(cudaEventCreate(&c->ev_compute_start[i]));
+        RING_CUDA(cudaEventCreate(&c->ev_compute_done[i]));
+    }
+    DeviceState* st = nullptr;
+    return device_state(&st);
+}
+
+int grow(void** buf, size_t* cap, size_t need) {
+    if (need <= *cap) return RING_OK;
+    // Growing is rare (first call, or a larger shape than any before) and synchronises the device.
+    RING_CUDA(cudaDeviceSynchronize());
+    if (*buf) RING_CUDA(cudaFree(*buf));
+    *buf = nullptr;
+    *cap = 0;
+    RING_CUDA(cudaMalloc(buf, need));
+    *cap = need;
+    return RING_OK;
+}
+
+}  // namespace
+
+// The reference's set_params_fprop (csrc/ring_attention.cu:361-395) with the same leading arguments.
+// It only fills the struct: no allocation, no copy (the reference does three of each per call).
+void set_params_fprop(Ring_fwd_params& params, const void* q, const void* k, const void* v, float* out, int npes,
+                      int mype, const int* seqlen, int dim, int max_seq) {
+    (void)max_seq;  // receive buffers are sized from seqlen[] by the context
+    std::memset(&params, 0, sizeof(params));
+    params.mype = mype;
+    params.npes = npes;
+    params.seqlen = nullptr;
+    params.h_seqlen = const_cast<int*>(seqlen);
+    params.dim = dim;
+    params.softmax_scale = dim > 0 ? 1.0f / std::sqrt(static_cast<float>(dim)) : 1.0f;
+    params.q_ptr = const_cast<void*>(q);
+    params.k_ptr = const_cast<void*>(k);
+    params.v_ptr = const_cast<void*>(v);
+    params.out_ptr = out;
+    params.k_buffer = nullptr;
+    params.v_buffer = nullptr;
+    params.batch = 1;
+    params.heads = 1;
+    params.lse_ptr = nullptr;
+    params.causal = 0;
+    params.is_bf16 = 0;
+    params.stream = 0;
+}
+
+// The ring loop.  Named after the reference's launcher (csrc/ring_attention.cu:669-704); the template
+// parameter of the reference (kernel traits) is chosen at run time from params.dim by launch_block().
+int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
+    const int P = p.npes;
+    const int r = p.mype;
+    const int B = p.batch > 0 ? p.batch : 1;
+    const int H = p.heads > 0 ? p.heads : 1;
+    const int S = p.h_seqlen[r];
+    const int D = p.dim;
+    const size_t shard_bytes = static_cast<size_t>(B) * H * S * D * 2;  // one of K or V
+    const int64_t rows = static_cast<int64_t>(B) * H * S;
+    const bool causal = p.causal != 0;
+    const bool skip_x = causal && c->causal_skip;
+    int rc;
+
+    if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * shard_bytes))) return rc;
+    if (P > 2 && (rc = grow(&c->recv[1], &c->recv_cap[1], 2 * shard_bytes))) return rc;
+    float* lse = static_cast<float*>(p.lse_ptr);
+    if (!lse) {
+        if ((rc = grow(reinterpret_cast<void**>(&c->lse_own), &c->lse_own_cap, rows * sizeof(float)))) return rc;
+        lse = c->lse_own;
+    }
+    if (P > 1 && c->merge_mode == RING_MERGE_SEPARATE_KERNEL) {
+        if ((rc = grow(reinterpret_cast<void**>(&c->o_part), &c->o_part_cap, rows * D * sizeof(float)))) return rc;
+        if ((rc = grow(reinterpret_cast<void**>(&c->lse_part), &c->lse_part_cap, rows * sizeof(float)))) return rc;
+    }
+
+    // The exchange stream may touch K/V only once the compute stream's earlier work (which may have
+    // produced them) is done.
+    if (P > 1) {
+        RING_CUDA(cudaEventRecord(c->ev_fork, stream));
+        RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_fork, 0));
+    }
+
+    c->last_steps = P;
+    bool have_partial = false;
+    for (int s = 0; s < P; ++s) {
+        const int src = (r + s) % P;  // csrc/ring_attention.cu:463
+
+        // ---- exchange s: bring the shard of step s + 1 into recv[s & 1] while step s computes --------
+        c->step_exchanged[s] = false;
+        if (s < P - 1) {
+            const int nsrc = (r + s + 1) % P;      // whose shard arrives
+            const int ndst = (r - s - 1 + 2 * P) % P;  // who gets this rank's shard
+            const bool do_recv = !skip_x || nsrc < r;  // a causal rank only reads shards at or before its own
+            const bool do_send = !skip_x || ndst > r;
+            if (s >= 2) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
+            if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_comm_start[s], c->comm_stream));
+            char* dst_k = static_cast<char*>(c->recv[s & 1]);
+            char* dst_v = dst_k + shard_bytes;
+            if (c->local) {
+                if (do_recv) {
+                    if (!c->local_k[nsrc] || !c->local_v[nsrc])
+                        return fail(RING_ERR_INVALID_ARGUMENT, "local shard %d was not registered", nsrc);
+                    RING_CUDA(cudaMemcpyAsync(dst_k, c->local_k[nsrc], shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                    RING_CUDA(cudaMemcpyAsync(dst_v, c->local_v[nsrc], shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                }
+            } else if (do_recv || do_send) {
+                NcclApi& n = nccl();
+                RING_NCCL(n.GroupStart());
+                if (do_send) {
+                    RING_NCCL(n.Send(p.k_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream));
+                    RING_NCCL(n.Send(p.v_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream));
+                }
+                if (do_recv) {
+                    RING_NCCL(n.Recv(dst_k, shard_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
+                    RING_NCCL(n.Recv(dst_v, shard_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
+                }
+                RING_NCCL(n.GroupEnd());
+            }
+            c->step_exchanged[s] = do_recv || do_send;
+            RING_CUDA(cudaEventRecord(c->ev_recv_done[s], c->comm_stream));
+        }
+
+        // ---- compute step s ----------------------------------------------------------------------------
+        if (s >= 1) RING_CUDA(cudaStreamWaitEvent(stream, c->ev_recv_done[s - 1], 0));
+        if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_compute_start[s], stream));
+        const bool compute = !(causal && src > r);  // a shard strictly after this rank's rows is fully masked
+        c->step_computed[s] = compute;
+        if (compute) {
+            BlockLaunch L;
+            L.q = p.q_ptr;
+            L.k = s == 0 ? p.k_ptr : c->recv[(s - 1) & 1];
+            L.v = s == 0 ? p.v_ptr : static_cast<char*>(c->recv[(s - 1) & 1]) + shard_bytes;
+            L.batch = B;
+            L.heads = H;
+            L.sq = S;
+            L.sk = S;
+            L.dim = D;
+            L.scale = p.softmax_scale;
+            L.causal = causal;
+            L.q_off = static_cast<int64_t>(r) * S;
+            L.k_off = static_cast<int64_t>(src) * S;
+            L.is_bf16 = p.is_bf16;
+            if (!have_partial || c->merge_mode == RING_MERGE_FUSED_EPILOGUE) {
+                L.o = static_cast<float*>(p.out_ptr);
+                L.lse = lse;
+                L.merge = have_partial ? 1 : 0;
+                if ((rc = launch_block(L, stream))) return rc;
+            } else {
+                L.o = c->o_part;
+                L.lse = c->lse_part;
+                L.merge = 0;
+                if ((rc = launch_block(L, stream))) return rc;
+                if ((rc = launch_merge(static_cast<float*>(p.out_ptr), lse, c->o_part, c->lse_part, rows, D, stream)))
+                    return rc;
+            }
+            have_partial = true;
+        }
+        RING_CUDA(cudaEventRecord(c->ev_compute_done[s], stream));
+    }
+    return RING_OK;
+}
+
+namespace {
+
+int validate_params(RingCtx* c, const Ring_fwd_params* p) {
+    if (!c) return fail(RING_ERR_INVALID_ARGUMENT, "null context");
+    if (!p) return fail(RING_ERR_INVALID_ARGUMENT, "null params");
+    if (!p->q_ptr || !p->k_ptr || !p->v_ptr || !p->out_ptr) return fail(RING_ERR_INVALID_ARGUMENT, "null tensor pointer");
+    if (p->npes != c->world)
+        return fail(RING_ERR_INVALID_ARGUMENT, "params.npes (%d) differs from the context's world size (%d)", p->npes, c->world);
+    if (p->mype < 0 || p->mype >= p->npes) return fail(RING_ERR_INVALID_ARGUMENT, "params.mype out of range");
+    if (!c->local && p->mype != c->rank)
+        return fail(RING_ERR_INVALID_ARGUMENT, "params.mype (%d) differs from the context's rank (%d)", p->mype, c->rank);
+    if (p->dim != 64 && p->dim != 128) return fail(RING_ERR_INVALID_ARGUMENT, "dim must be 64 or 128, got %d", p->dim);
+    if (!p->h_seqlen) return fail(RING_ERR_INVALID_ARGUMENT, "params.h_seqlen (host sequence-length table) is null");
+    for (int i = 0; i < p->npes; ++i)
+        if (p->h_seqlen[i] != p->h_seqlen[0])
+            return fail(RING_ERR_INVALID_ARGUMENT, "uneven shards are not supported (seqlen[%d] = %d, seqlen[0] = %d)", i,
+                        p->h_seqlen[i], p->h_seqlen[0]);
+    if (p->h_seqlen[0] <= 0 || p->h_seqlen[0] % 128 != 0)
+        return fail(RING_ERR_INVALID_ARGUMENT, "seqlen per rank must be a positive multiple of 128, got %d", p->h_seqlen[0]);
+    if (!(p->softmax_scale > 0.f) || !std::isfinite(p->softmax_scale))
+        return fail(RING_ERR_INVALID_ARGUMENT, "softmax_scale must be positive and finite");
+    int dev = -1;
+    RING_CUDA(cudaGetDevice(&dev));
+    if (dev != c->device)
+        return fail(RING_ERR_INVALID_ARGUMENT, "current device %d is not the context's device %d", dev, c->device);
+    return RING_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ C ABI
+extern "C" {
+
+const char* ring_last_error_string(void) { return g_last_error.c_str(); }
+
+int64_t ring_kernel_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int ring_device_status(int* status_out) {
+    if (!status_out) return fail(RING_ERR_INVALID_ARGUMENT, "null status_out");
+    return read_status(status_out);
+}
+
+int ring_device_status_reset(void) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    RING_CUDA(cudaDeviceSynchronize());
+    RING_CUDA(cudaMemset(st->d_status, 0, sizeof(int)));
+    return RING_OK;
+}
+
+int ring_get_unique_id(void* id_out) {
+    if (!id_out) return fail(RING_ERR_INVALID_ARGUMENT, "null id_out");
+    NcclApi& n = nccl();
+    if (!n.ok) return fail(RING_ERR_NCCL, "libnccl.so.2 could not be loaded");
+    static_assert(sizeof(ncclUniqueId) <= RING_UNIQUE_ID_BYTES, "unique id size");
+    ncclUniqueId id;
+    RING_NCCL(n.GetUniqueId(&id));
+    std::memset(id_out, 0, RING_UNIQUE_ID_BYTES);
+    std::memcpy(id_out, &id, sizeof(id));
+    return RING_OK;
+}
+
+int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id) {
+    if (!ctx) return fail(RING_ERR_INVALID_ARGUMENT, "null ctx");
+    *ctx = nullptr;
+    if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+        return fail(RING_ERR_INVALID_ARGUMENT, "bad rank/world %d/%d", rank, world);
+    if (world > 1 && !unique_id) return fail(RING_ERR_INVALID_ARGUMENT, "world > 1 needs a unique id");
+    RingCtx* c = new RingCtx();
+    c->rank = rank;
+    c->world = world;
+    int rc = ctx_common_init(c);
+    if (rc) { delete c; return rc; }
+    if (world > 1) {
+        NcclApi& n = nccl();
+        if (!n.ok) { delete c; return fail(RING_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
+        ncclUniqueId id;
+        std::memcpy(&id, unique_id, sizeof(id));
+        ncclResult_t r = n.CommInitRank(&c->comm, world, id, rank);
+        if (r != ncclSuccess) {
+            delete c;
+            return fail(RING_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString(r));
+        }
+    }
+    *ctx = c;
+    return RING_OK;
+}
+
+int ring_ctx_create_local(RingCtx** ctx, int world) {
+    if (!ctx) return fail(RING_ERR_INVALID_ARGUMENT, "null ctx");
+    *ctx = nullptr;
+    if (world < 1 || world > kMaxWorld) return fail(RING_ERR_INVALID_ARGUMENT, "bad world %d", world);
+    RingCtx* c = new RingCtx();
+    c->rank = 0;
+    c->world = world;
+    c->local = true;
+    int rc = ctx_common_init(c);
+    if (rc) { delete c; return rc; }
+    *ctx = c;
+    return RING_OK;
+}
+
+int ring_ctx_set_local_shards(RingCtx* ctx, const void* const* k_shards, const void* const* v_shards) {
+    if (!ctx || !ctx->local || !k_shards || !v_shards)
+        return fail(RING_ERR_INVALID_ARGUMENT, "needs a local context and two pointer tables");
+    for (int i = 0; i < ctx->world; ++i) {
+        ctx->local_k[i] = k_shards[i];
+        ctx->local_v[i] = v_shards[i];
+    }
+    return RING_OK;
+}
+
+int ring_ctx_set_option(RingCtx* ctx, int option, int value) {
+    if (!ctx) return fail(RING_ERR_INVALID_ARGUMENT, "null context");
+    switch (option) {
+        case RING_OPT_MERGE_MODE:
+            if (value != RING_MERGE_SEPARATE_KERNEL && value != RING_MERGE_FUSED_EPILOGUE)
+                return fail(RING_ERR_INVALID_ARGUMENT, "bad merge mode %d", value);
+            ctx->merge_mode = value;
+            return RING_OK;
+        case RING_OPT_CAUSAL_SKIP_EXCHANGE:
+            ctx->causal_skip = value ? 1 : 0;
+            return RING_OK;
+        case RING_OPT_RECORD_TIMINGS:
+            ctx->record_timings = value ? 1 : 0;
+            return RING_OK;
+        default:
+            return fail(RING_ERR_INVALID_ARGUMENT, "unknown option %d", option);
+    }
+}
+
+int ring_ctx_destroy(RingCtx* c) {
+    if (!c) return RING_OK;
+    if (g_default_ctx == c) g_default_ctx = nullptr;
+    cudaDeviceSynchronize();
+    if (c->comm) nccl().CommDestroy(c->comm);
+    for (int i = 0; i < c->world; ++i) {
+        if (c->ev_recv_done[i]) cudaEventDestroy(c->ev_recv_done[i]);
+        if (c->ev_comm_start[i]) cudaEventDestroy(c->ev_comm_start[i]);
+        if (c->ev_compute_start[i]) cudaEventDestroy(c->ev_compute_start[i]);
+        if (c->ev_compute_done[i]) cudaEventDestroy(c->ev_compute_done[i]);
+    }
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    if (c->comm_stream) cudaStreamDestroy(c->comm_stream);
+    for (int i = 0; i < 2; ++i)
+        if (c->recv[i]) cudaFree(c->recv[i]);
+    if (c->o_part) cudaFree(c->o_part);
+    if (c->lse_part) cudaFree(c->lse_part);
+    if (c->lse_own) cudaFree(c->lse_own);
+    delete c;
+    return RING_OK;
+}
+
+int ring_set_default_ctx(RingCtx* ctx) {
+    g_default_ctx = ctx;
+    return RING_OK;
+}
+
+int ring_attention_fwd(RingCtx* ctx, const struct Ring_fwd_params* params) {
+    int rc = validate_params(ctx, params);
+    if (rc) return rc;
+    return run_ring_fwd(ctx, *params, params->stream);
+}
+
+int ring_ctx_synchronize(RingCtx* ctx) {
+    if (!ctx) return fail(RING_ERR_INVALID_ARGUMENT, "null context");
+    int status = 0;
+    int rc = read_status(&status);
+    if (rc) return rc;
+    if (ctx->comm) {
+        ncclResult_t async = ncclSuccess;
+        RING_NCCL(nccl().CommGetAsyncError(ctx->comm, &async));
+        if (async != ncclSuccess) return fail(RING_ERR_NCCL, "NCCL async error: %s", nccl().GetErrorString(async));
+    }
+    if (status != 0) return fail(RING_ERR_DEVICE_TIMEOUT, "a bounded wait inside a kernel ran out (device status %d)", status);
+    return RING_OK;
+}
+
+int ring_ctx_get_timings(RingCtx* c, float* compute_ms, float* comm_ms, float* exposed_ms, int n) {
+    if (!c || !compute_ms || !comm_ms || !exposed_ms) return fail(RING_ERR_INVALID_ARGUMENT, "null argument");
+    if (!c->record_timings) return fail(RING_ERR_INVALID_ARGUMENT, "RING_OPT_RECORD_TIMINGS is off");
+    if (n < c->last_steps) return fail(RING_ERR_INVALID_ARGUMENT, "arrays too short: %d < %d", n, c->last_steps);
+    const int P = c->last_steps;
+    for (int s = 0; s < P; ++s) {
+        compute_ms[s] = comm_ms[s] = exposed_ms[s] = 0.f;
+        RING_CUDA(cudaEventElapsedTime(&compute_ms[s], c->ev_compute_start[s], c->ev_compute_done[s]));
+        if (s < P - 1) {
+            RING_CUDA(cudaEventElapsedTime(&comm_ms[s], c->ev_comm_start[s], c->ev_recv_done[s]));
+            // idle gap of the compute stream between the end of step s and the start of step s + 1
+            RING_CUDA(cudaEventElapsedTime(&exposed_ms[s], c->ev_compute_done[s], c->ev_compute_start[s + 1]));
+        }
+    }
+    return RING_OK;
+}
+
+int ring_attention_block_fwd(const void* q, const void* k, const void* v, float* o, float* lse, int batch, int heads,
+                             int sq, int sk, int dim, float softmax_scale, int causal, int64_t q_off, int64_t k_off,
+                             int merge, int is_bf16, void* stream) {
+    BlockLaunch L;
+    L.q = q; L.k = k; L.v = v; L.o = o; L.lse = lse;
+    L.batch = batch; L.heads = heads; L.sq = sq; L.sk = sk; L.dim = dim;
+    L.scale = softmax_scale; L.causal = causal; L.q_off = q_off; L.k_off = k_off;
+    L.merge = merge; L.is_bf16 = is_bf16;
+    return launch_block(L, static_cast<cudaStream_t>(stream));
+}
+
+int ring_lse_merge(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part, int64_t rows, int dim,
+                   void* stream) {
+    return launch_merge(o_acc, lse_acc, o_part, lse_part, rows, dim, static_cast<cudaStream_t>(stream));
+}
+
+int ring_attention_scaled(const void* q, const void* k, const void* v, float* out, int npes, int mype,
+                          const int* seqlen, int dim, int max_seq, float softmax_scale) {
+    if (!seqlen) return fail(RING_ERR_INVALID_ARGUMENT, "null seqlen table");
+    if (npes < 1 || mype < 0 || mype >= npes) return fail(RING_ERR_INVALID_ARGUMENT, "bad npes/mype %d/%d", npes, mype);
+    if (max_seq > 0 && seqlen[mype] > max_seq) return fail(RING_ERR_INVALID_ARGUMENT, "seqlen exceeds max_seq");
+    RingCtx* c = g_default_ctx;
+    if (!c) {
+        if (npes > 1)
+            return fail(RING_ERR_NO_CONTEXT, "ring_attention with npes > 1 needs ring_set_default_ctx() first");
+        if (!g_solo_ctx) {
+            int rc = ring_ctx_create(&g_solo_ctx, 0, 1, nullptr);
+            if (rc) return rc;
+        }
+        c = g_solo_ctx;
+    }
+    Ring_fwd_params params;
+    set_params_fprop(params, q, k, v, out, npes, mype, seqlen, dim, max_seq);
+    params.softmax_scale = softmax_scale;
+    int rc = ring_attention_fwd(c, &params);
+    if (rc) return rc;
+    return ring_ctx_synchronize(c);  // the reference call is synchronous (csrc/ring_attention.cu:721)
+}
+
+int ring_attention(const void* q, const void* k, const void* v, float* out, int npes, int mype, const int* seqlen,
+                   int dim, int max_seq) {
+    const float scale = dim > 0 ? 1.0f / std::sqrt(static_cast<float>(dim)) : 1.0f;
+    return ring_attention_scaled(q, k, v, out, npes, mype, seqlen, dim, max_seq, scale);
+}
+
+}  // extern "C"
