@@ -131,6 +131,39 @@ int ring_attention_block_fwd(const void* q, const void* k, const void* v, float*
 int ring_lse_merge(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part, int64_t rows,
                    int dim, void* stream);
 
+/*
+ * No counterpart in the reference (which allocates inside every call, csrc/ring_attention.cu:384-393).
+ *
+ * Attention of q [B,H,Sq,D] against k/v [B,H,Sk,D] taken kv_chunk key rows at a time: the first chunk
+ * writes o / lse, every further chunk is computed into a scratch partial and folded in by the merge
+ * kernel -- the same two kernels and the same arithmetic as one ring step followed by ring_lse_merge,
+ * so the result equals ring_attention_block_fwd over the whole K/V up to merge rounding.  Causal masks
+ * keys with index j > i (row 0 of q and of k are the same sequence position).
+ *
+ * This variant exists for hosts that hand a component its tensors but do not let it obtain device memory
+ * of its own: a serving runtime that reserved the whole GPU at start-up and gives plug-ins no allocator,
+ * or a process pinned to a fixed memory budget, where cudaMalloc either fails or stalls every stream with
+ * its implicit synchronisation.  The function calls no cudaMalloc / cudaFree and no allocating library
+ * routine.  Its scratch is a fixed array inside this library's device image (about 16.3 MiB, held by
+ * every GPU that loads the library until the process exits), which bounds the problem size:
+ *     batch * heads * sq        <= RING_STATIC_MAX_ROWS        (65536 rows)
+ *     batch * heads * sq * dim  <= RING_STATIC_MAX_OUT_ELEMS   (4 Mi floats)
+ * Larger calls are refused with RING_ERR_INVALID_ARGUMENT and a message naming the limit.
+ * The first call on a device resolves the array's device address (cudaGetSymbolAddress) and sets the
+ * kernel's shared-memory attribute; make that first call before any stream capture begins.
+ * All calls on a device share the one array and it keeps the last call's contents: the function clears
+ * the status word it needs at zero itself, but two calls whose kernels overlap on the GPU (different
+ * streams, no ordering between them) race on the partials and give wrong results.  Serialise them.
+ * A bounded wait that runs out inside a kernel of this path is recorded in the array's own status word,
+ * not in the word ring_device_status() reads.
+ * Asynchronous on `stream` (cudaStream_t as void*).
+ */
+#define RING_STATIC_MAX_ROWS 65536
+#define RING_STATIC_MAX_OUT_ELEMS (4 * 1024 * 1024)
+int ring_attention_chunked_fwd_static(const void* q, const void* k, const void* v, float* o, float* lse,
+                                      int batch, int heads, int sq, int sk, int dim, float softmax_scale,
+                                      int causal, int kv_chunk, int is_bf16, void* stream);
+
 /* Device status word of the current device: 0, or the code of the bounded wait that ran out
  * (1xx, see csrc/block_attention.cuh).  ring_device_status synchronises the device. */
 int ring_device_status(int* status_out);

@@ -23,6 +23,8 @@ RING_MERGE_FUSED_EPILOGUE = 1
 RING_OPT_MERGE_MODE = 1
 RING_OPT_CAUSAL_SKIP_EXCHANGE = 2
 RING_OPT_RECORD_TIMINGS = 3
+RING_STATIC_MAX_ROWS = 65536
+RING_STATIC_MAX_OUT_ELEMS = 4 * 1024 * 1024
 
 
 class Ring_fwd_params(ctypes.Structure):
@@ -55,6 +57,8 @@ SYMBOLS = {
     "ring_attention_block_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_float, c_int, c_int64, c_int64, c_int, c_int, c_void_p]),
     "ring_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "ring_attention_chunked_fwd_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                  c_float, c_int, c_int, c_int, c_void_p]),
     "ring_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "ring_device_status_reset": (c_int, []),
     "ring_kernel_launch_count": (c_int64, []),

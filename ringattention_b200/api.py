@@ -22,6 +22,7 @@ from ._lib import Ring_fwd_params, check
 __all__ = [
     "ring_attention", "ring_attention_scaled", "set_params_fprop", "Ring_fwd_params", "RingContext",
     "attention_block_fwd", "lse_merge", "device_status", "device_status_reset", "kernel_launch_count",
+    "attention_chunked_fwd_static",
 ]
 
 
@@ -242,3 +243,25 @@ def device_status_reset() -> None:
 
 def kernel_launch_count() -> int:
     return int(_lib.load().ring_kernel_launch_count())
+
+
+def attention_chunked_fwd_static(q, k, v, o, lse, kv_chunk: int, *, softmax_scale: Optional[float] = None,
+                                 causal: bool = False, stream=None) -> None:
+    """Attention of q [B,H,Sq,D] against k/v [B,H,Sk,D], `kv_chunk` key rows at a time, for hosts that do
+    not let this library allocate device memory (a runtime that owns the whole GPU, a fixed memory budget).
+    Nothing is allocated: the partial of each chunk lives in a fixed ~16 MiB array inside the library, so
+    B*H*Sq <= 65536 rows and B*H*Sq*D <= 4 Mi floats, and calls that overlap on the GPU would race on it.
+    The first call on a device also does the one-time set-up; make it before any stream capture."""
+    import torch
+    B, H, Sq, D = q.shape
+    Sk = k.shape[2]
+    if tuple(k.shape) != (B, H, Sk, D) or tuple(v.shape) != (B, H, Sk, D):
+        raise ValueError("k, v must be [B, H, Sk, D]")
+    if tuple(o.shape) != (B, H, Sq, D) or tuple(lse.shape) != (B, H, Sq):
+        raise ValueError("o must be [B, H, Sq, D] and lse [B, H, Sq]")
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(D)
+    check(_lib.load().ring_attention_chunked_fwd_static(
+        _ptr(q, "q", _half_types()), _ptr(k, "k", _half_types()), _ptr(v, "v", _half_types()),
+        _ptr(o, "o", (torch.float32,)), _ptr(lse, "lse", (torch.float32,)), B, H, Sq, Sk, D, scale,
+        int(bool(causal)), int(kv_chunk), int(q.dtype == torch.bfloat16), _stream_handle(stream)),
+        "ring_attention_chunked_fwd_static")

@@ -746,3 +746,178 @@ int ring_attention(const void* q, const void* k, const void* v, float* out, int 
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------ no-allocation entry point
+// Chunked attention whose partial-result scratch lives in a fixed device array of this library instead
+// of in memory obtained from the CUDA allocator.  See include/ring_attention_b200.h for who needs it.
+//
+// Layout of the array (floats): [0, 64) header, word 0 = device status of this path;
+// [64, 64 + 65536) row LSE of the partial; then 4 Mi floats for the partial output.
+namespace {
+
+constexpr int64_t kStaticHeaderFloats = 64;
+constexpr int64_t kStaticMaxRows = RING_STATIC_MAX_ROWS;
+constexpr int64_t kStaticMaxOutElems = RING_STATIC_MAX_OUT_ELEMS;
+
+}  // namespace
+
+static __device__ __align__(256) float g_static_scratch[kStaticHeaderFloats + kStaticMaxRows + kStaticMaxOutElems];
+
+namespace {
+
+struct StaticSetup {
+    float* base = nullptr;  // DEVICE address of g_static_scratch on this device (the symbol itself is a host-side stand-in)
+    bool attr_set[2][2] = {{false, false}, {false, false}};
+};
+std::mutex g_static_mutex;
+StaticSetup g_static[64];
+
+// Once per device, with that device current: resolve the device address of the array.
+int static_setup(StaticSetup** out) {
+    int dev = 0;
+    RING_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(RING_ERR_UNSUPPORTED, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    StaticSetup& s = g_static[dev];
+    if (!s.base) {
+        void* p = nullptr;
+        RING_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return fail(RING_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        s.base = static_cast<float*>(p);
+    }
+    *out = &s;
+    return RING_OK;
+}
+
+// Tensor map over `rows` rows of a [batch, heads, rows_total, dim] tensor starting at `base` (which may
+// point into the middle of the sequence): the head and batch strides are those of the whole tensor.
+int make_tensor_map_strided(CUtensorMap* tm, const void* base, int batch, int heads, int rows, int64_t rows_total, int dim,
+                            bool bf16) {
+    EncodeTiledFn enc = nullptr;
+    int rc = encode_fn(&enc);
+    if (rc) return rc;
+    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(rows),
+                                static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(rows_total) * dim * 2,
+                                   static_cast<cuuint64_t>(heads) * rows_total * dim * 2};
+    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
+                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(RING_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return RING_OK;
+}
+
+struct StaticChunk {
+    const void *q, *k, *v;  // k, v already advanced to the first row of the chunk
+    float* o;
+    float* lse;
+    int batch, heads, sq, sk_total, rows, dim;
+    float scale;
+    int causal;
+    int64_t k_off;
+    int is_bf16;
+};
+
+template <class Traits>
+int launch_block_static(const StaticChunk& c, StaticSetup* s, cudaStream_t stream) {
+    auto kernel = &ring::ring_block_attention_kernel<Traits>;
+    bool& attr = s->attr_set[Traits::kHeadDim == 128][Traits::kIsBf16];
+    if (!attr) {
+        RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
+        attr = true;
+    }
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map_strided(&tq, c.q, c.batch, c.heads, c.sq, c.sq, c.dim, c.is_bf16))) return rc;
+    if ((rc = make_tensor_map_strided(&tk, c.k, c.batch, c.heads, c.rows, c.sk_total, c.dim, c.is_bf16))) return rc;
+    if ((rc = make_tensor_map_strided(&tv, c.v, c.batch, c.heads, c.rows, c.sk_total, c.dim, c.is_bf16))) return rc;
+    ring::BlockFwdArgs a;
+    a.o = c.o;
+    a.lse = c.lse;
+    a.o_row_stride = c.dim;
+    a.o_head_stride = static_cast<int64_t>(c.sq) * c.dim;
+    a.o_batch_stride = a.o_head_stride * c.heads;
+    a.lse_head_stride = c.sq;
+    a.lse_batch_stride = static_cast<int64_t>(c.sq) * c.heads;
+    a.heads = c.heads;
+    a.sq = c.sq;
+    a.sk = c.rows;
+    a.scale = c.scale;
+    a.scale_log2 = c.scale * 1.4426950408889634f;
+    a.causal = c.causal ? 1 : 0;
+    a.diag = static_cast<int>(-c.k_off);
+    a.merge = 0;
+    a.status = reinterpret_cast<int*>(s->base);  // header word 0
+    dim3 grid((c.sq + Traits::kBlockM - 1) / Traits::kBlockM, c.batch * c.heads);
+    kernel<<<grid, dim3(Traits::kNThreads), Traits::kSmemSize, stream>>>(tq, tk, tv, a);
+    RING_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RING_OK;
+}
+
+}  // namespace
+
+extern "C" int ring_attention_chunked_fwd_static(const void* q, const void* k, const void* v, float* o, float* lse,
+                                                 int batch, int heads, int sq, int sk, int dim, float softmax_scale,
+                                                 int causal, int kv_chunk, int is_bf16, void* stream_) {
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    BlockLaunch whole;
+    whole.q = q; whole.k = k; whole.v = v; whole.o = o; whole.lse = lse;
+    whole.batch = batch; whole.heads = heads; whole.sq = sq; whole.sk = sk; whole.dim = dim;
+    whole.scale = softmax_scale; whole.causal = causal; whole.q_off = 0; whole.k_off = 0; whole.merge = 0;
+    whole.is_bf16 = is_bf16;
+    int rc = validate_block(whole);
+    if (rc) return rc;
+    if (kv_chunk <= 0 || kv_chunk % 128 != 0)
+        return fail(RING_ERR_INVALID_ARGUMENT, "kv_chunk must be a positive multiple of 128, got %d", kv_chunk);
+    const int64_t rows = static_cast<int64_t>(batch) * heads * sq;
+    if (rows > kStaticMaxRows || rows * dim > kStaticMaxOutElems)
+        return fail(RING_ERR_INVALID_ARGUMENT,
+                    "batch*heads*sq = %lld rows (x dim = %lld floats) exceeds the fixed scratch of this entry point "
+                    "(%lld rows, %lld floats)", (long long)rows, (long long)(rows * dim), (long long)kStaticMaxRows,
+                    (long long)kStaticMaxOutElems);
+    StaticSetup* s = nullptr;
+    if ((rc = static_setup(&s))) return rc;
+    float* lse_part = s->base + kStaticHeaderFloats;
+    float* o_part = lse_part + kStaticMaxRows;
+    // The array keeps whatever the previous call left: the status word must start at zero (a stale error
+    // would make every CTA return at once).  The partials need no clearing: every row is written by the
+    // block kernel before the merge reads it.
+    RING_CUDA(cudaMemsetAsync(s->base, 0, sizeof(int), stream));
+
+    for (int c0 = 0; c0 < sk; c0 += kv_chunk) {
+        StaticChunk c;
+        c.q = q;
+        c.k = static_cast<const char*>(k) + static_cast<size_t>(c0) * dim * 2;
+        c.v = static_cast<const char*>(v) + static_cast<size_t>(c0) * dim * 2;
+        c.batch = batch; c.heads = heads; c.sq = sq; c.sk_total = sk;
+        c.rows = (sk - c0) < kv_chunk ? (sk - c0) : kv_chunk;
+        c.dim = dim; c.scale = softmax_scale; c.causal = causal; c.k_off = c0; c.is_bf16 = is_bf16;
+        c.o = c0 == 0 ? o : o_part;
+        c.lse = c0 == 0 ? lse : lse_part;
+        if (dim == 128) {
+            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<128, 256, 128, 10, __nv_bfloat16>>(c, s, stream)
+                         : launch_block_static<Ring_fwd_traits<128, 256, 128, 10, __half>>(c, s, stream);
+        } else {
+            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<64, 256, 128, 10, __nv_bfloat16>>(c, s, stream)
+                         : launch_block_static<Ring_fwd_traits<64, 256, 128, 10, __half>>(c, s, stream);
+        }
+        if (rc) return rc;
+        if (c0 > 0) {
+            // same grid sizing as launch_merge(), without the device-attribute query
+            const int threads = 256;
+            const int64_t want = (rows + 7) / 8;
+            const int blocks = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+            if (dim == 128)
+                ring::ring_lse_merge_kernel<128><<<blocks, threads, 0, stream>>>(o, lse, o_part, lse_part, rows);
+            else
+                ring::ring_lse_merge_kernel<64><<<blocks, threads, 0, stream>>>(o, lse, o_part, lse_part, rows);
+            RING_CUDA(cudaGetLastError());
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+        }
+    }
+    return RING_OK;
+}
