@@ -98,6 +98,23 @@ int ring_ctx_set_local_shards(RingCtx* ctx, const void* const* k_shards, const v
  */
 int ring_attention_fwd(RingCtx* ctx, const struct Ring_fwd_params* params);
 
+/*
+ * The schedule run_ring_fwd follows, as pure host logic (no GPU needed): step `step` of rank `rank`.
+ * Restates the loop header of ring_attention_kernel (csrc/ring_attention.cu:456-470, 611-619): the shard
+ * visited at step i is that of PE (mype + i) % npes, fetched from its origin PE.
+ */
+typedef struct RingStepPlan {
+    int src_rank;       /* whose K/V shard this step attends to */
+    int compute;        /* 0 if the shard is fully masked for this rank (causal) */
+    int compute_buffer; /* -1: the rank's own shard; else index of the receive buffer holding the shard */
+    int recv_buffer;    /* receive buffer the concurrent exchange fills (step & 1) */
+    int recv_from;      /* origin rank of the shard for step + 1, or -1 on the last step */
+    int send_to;        /* rank that receives this rank's shard meanwhile, or -1 */
+    int do_recv;        /* 0 if the arriving shard would never be read (causal skip) */
+    int do_send;
+} RingStepPlan;
+int ring_step_plan(int world, int rank, int step, int causal, int causal_skip_exchange, RingStepPlan* out);
+
 /* Blocks until everything the context has enqueued is done and returns the device status
  * (RING_OK or RING_ERR_DEVICE_TIMEOUT / RING_ERR_CUDA). */
 int ring_ctx_synchronize(RingCtx* ctx);

@@ -40,6 +40,11 @@ class Ring_fwd_params(ctypes.Structure):
     ]
 
 
+class RingStepPlan(ctypes.Structure):
+    _fields_ = [(n, c_int) for n in ("src_rank", "compute", "compute_buffer", "recv_buffer", "recv_from", "send_to",
+                                     "do_recv", "do_send")]
+
+
 # name -> (restype, argtypes); every symbol declared in include/ring_attention_b200.h
 SYMBOLS = {
     "ring_attention": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.POINTER(c_int), c_int, c_int]),
@@ -53,6 +58,7 @@ SYMBOLS = {
     "ring_ctx_set_local_shards": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),
     "ring_attention_fwd": (c_int, [c_void_p, ctypes.POINTER(Ring_fwd_params)]),
     "ring_ctx_synchronize": (c_int, [c_void_p]),
+    "ring_step_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(RingStepPlan)]),
     "ring_ctx_get_timings": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_float), ctypes.POINTER(c_float), c_int]),
     "ring_attention_block_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_float, c_int, c_int64, c_int64, c_int, c_int, c_void_p]),

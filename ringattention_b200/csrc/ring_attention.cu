@@ -390,6 +390,33 @@ void set_params_fprop(Ring_fwd_params& params, const void* q, const void* k, con
     params.stream = 0;
 }
 
+// One ring step of one rank, as pure host logic (no CUDA): which shard the step attends to, whether it
+// computes at all, what is exchanged meanwhile and through which receive buffer.  run_ring_fwd() follows
+// exactly this plan; it is exported so the schedule can be checked without a GPU.
+//   step s attends to the shard of rank (rank + s) % world            (csrc/ring_attention.cu:463)
+//   exchange s (s < world - 1) brings the shard of step s + 1 into recv buffer s & 1, pulled from its
+//   ORIGIN rank (csrc/ring_attention.cu:613-617), while this rank's shard goes to (rank - s - 1) mod world.
+extern "C" int ring_step_plan(int world, int rank, int step, int causal, int causal_skip_exchange, RingStepPlan* out) {
+    if (!out) return fail(RING_ERR_INVALID_ARGUMENT, "null plan");
+    if (world < 1 || rank < 0 || rank >= world || step < 0 || step >= world)
+        return fail(RING_ERR_INVALID_ARGUMENT, "bad world/rank/step %d/%d/%d", world, rank, step);
+    const bool skip_x = causal && causal_skip_exchange;
+    out->src_rank = (rank + step) % world;
+    out->compute = !(causal && out->src_rank > rank);  // a shard strictly after this rank's rows is fully masked
+    out->compute_buffer = step == 0 ? -1 : ((step - 1) & 1);
+    out->recv_buffer = step & 1;
+    if (step < world - 1) {
+        out->recv_from = (rank + step + 1) % world;
+        out->send_to = (rank - step - 1 + 2 * world) % world;
+        out->do_recv = (!skip_x || out->recv_from < rank) ? 1 : 0;  // a causal rank only reads shards at or before its own
+        out->do_send = (!skip_x || out->send_to > rank) ? 1 : 0;
+    } else {
+        out->recv_from = out->send_to = -1;
+        out->do_recv = out->do_send = 0;
+    }
+    return RING_OK;
+}
+
 // The ring loop.  Named after the reference's launcher (csrc/ring_attention.cu:669-704); the template
 // parameter of the reference (kernel traits) is chosen at run time from params.dim by launch_block().
 int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
@@ -402,7 +429,6 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     const size_t shard_bytes = static_cast<size_t>(B) * H * S * D * 2;  // one of K or V
     const int64_t rows = static_cast<int64_t>(B) * H * S;
     const bool causal = p.causal != 0;
-    const bool skip_x = causal && c->causal_skip;
     int rc;
 
     if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * shard_bytes))) return rc;
@@ -427,18 +453,20 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     c->last_steps = P;
     bool have_partial = false;
     for (int s = 0; s < P; ++s) {
-        const int src = (r + s) % P;  // csrc/ring_attention.cu:463
+        RingStepPlan plan;
+        if ((rc = ring_step_plan(P, r, s, causal ? 1 : 0, c->causal_skip, &plan))) return rc;
+        const int src = plan.src_rank;
 
         // ---- exchange s: bring the shard of step s + 1 into recv[s & 1] while step s computes --------
         c->step_exchanged[s] = false;
         if (s < P - 1) {
-            const int nsrc = (r + s + 1) % P;      // whose shard arrives
-            const int ndst = (r - s - 1 + 2 * P) % P;  // who gets this rank's shard
-            const bool do_recv = !skip_x || nsrc < r;  // a causal rank only reads shards at or before its own
-            const bool do_send = !skip_x || ndst > r;
+            const int nsrc = plan.recv_from;  // whose shard arrives
+            const int ndst = plan.send_to;    // who gets this rank's shard
+            const bool do_recv = plan.do_recv != 0;
+            const bool do_send = plan.do_send != 0;
             if (s >= 2) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
             if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_comm_start[s], c->comm_stream));
-            char* dst_k = static_cast<char*>(c->recv[s & 1]);
+            char* dst_k = static_cast<char*>(c->recv[plan.recv_buffer]);
             char* dst_v = dst_k + shard_bytes;
             if (c->local) {
                 if (do_recv) {
@@ -467,13 +495,13 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         // ---- compute step s ----------------------------------------------------------------------------
         if (s >= 1) RING_CUDA(cudaStreamWaitEvent(stream, c->ev_recv_done[s - 1], 0));
         if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_compute_start[s], stream));
-        const bool compute = !(causal && src > r);  // a shard strictly after this rank's rows is fully masked
+        const bool compute = plan.compute != 0;
         c->step_computed[s] = compute;
         if (compute) {
             BlockLaunch L;
             L.q = p.q_ptr;
-            L.k = s == 0 ? p.k_ptr : c->recv[(s - 1) & 1];
-            L.v = s == 0 ? p.v_ptr : static_cast<char*>(c->recv[(s - 1) & 1]) + shard_bytes;
+            L.k = plan.compute_buffer < 0 ? p.k_ptr : c->recv[plan.compute_buffer];
+            L.v = plan.compute_buffer < 0 ? p.v_ptr : static_cast<char*>(c->recv[plan.compute_buffer]) + shard_bytes;
             L.batch = B;
             L.heads = H;
             L.sq = S;

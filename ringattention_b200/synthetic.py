@@ -57,3 +57,23 @@ def sample_rows(seed: int, B: int, H: int, S: int, n: int, always=()):
     rows = np.stack([rng.integers(0, B, n), rng.integers(0, H, n), rng.integers(0, S, n)], axis=1)
     extra = np.array([[0, 0, int(i)] for i in always if 0 <= int(i) < S], dtype=np.int64).reshape(-1, 3)
     return np.concatenate([extra, rows.astype(np.int64)], axis=0)
+
+
+def make_head(which: str, seed: int, H: int, D: int, b: int, h: int, row_start: int, rows: int,
+              gain: float = 1.0) -> np.ndarray:
+    """fp16 [rows, D]: rows [row_start, row_start + rows) of head (b, h) of global tensor `which`
+    (identical values to the same slice of make_shard)."""
+    tid = TENSOR_IDS[which]
+    out = np.empty((rows, D), dtype=np.float16)
+    bh = b * H + h
+    first_blk = row_start // ROW_BLOCK
+    last_blk = (row_start + rows - 1) // ROW_BLOCK if rows > 0 else first_blk - 1
+    for blk in range(first_blk, last_blk + 1):
+        vals = _stream(seed, tid, bh, blk).standard_normal((ROW_BLOCK, D), dtype=np.float32)
+        if gain != 1.0:
+            vals *= np.float32(gain)
+        g0 = blk * ROW_BLOCK
+        lo = max(g0, row_start)
+        hi = min(g0 + ROW_BLOCK, row_start + rows)
+        out[lo - row_start:hi - row_start, :] = vals[lo - g0:hi - g0, :]
+    return out
