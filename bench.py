@@ -181,6 +181,12 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     ctx.set_option(ra.RING_OPT_RECORD_TIMINGS, 1)
     if args.merge_mode is not None:
         ctx.set_option(ra.RING_OPT_MERGE_MODE, args.merge_mode)
+    if world > 1 and args.transport != "default":
+        ctx.set_option(ra.RING_OPT_TRANSPORT, ra.RING_TRANSPORT_NCCL if args.transport == "nccl" else ra.RING_TRANSPORT_PEER_COPY)
+    transport = "none (one rank)"
+    if world > 1:
+        transport = ("copy-engine pushes into IPC-shared receive buffers" if ctx.get_option(ra.RING_OPT_TRANSPORT) == ra.RING_TRANSPORT_PEER_COPY
+                     else "NCCL send/recv")
 
     # ---- inputs: this rank's rows of the global seeded tensors, in pinned host memory and on the device
     hq, hk, hv = (torch.from_numpy(x).pin_memory() for x in synthetic.make_qkv(SEED, B, H, D, rank * S_LOCAL, S_LOCAL))
@@ -284,7 +290,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": workload_name(world), "batch": B, "heads": H, "seq_local": S_LOCAL, "head_dim": D,
-                       "causal": False, "parallelism": f"ring{world} (sequence sharded, NCCL send/recv K/V exchange)",
+                       "causal": False, "parallelism": f"ring{world} (sequence sharded, double-buffered K/V exchange on a side stream)",
+                       "kv_transport": transport,
                        "l2": "inputs (192 MiB of Q,K,V per GPU) exceed the 126 MB L2; no flush between iterations",
                        "merge_mode": "separate kernel" if args.merge_mode == 0 else "fused epilogue"},
             "per_gpu_tflops": value / world,
@@ -320,6 +327,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--transport", default="default", choices=["default", "nccl", "peer"], help="K/V exchange transport")
     ap.add_argument("--merge-mode", type=int, default=None, choices=[0, 1], help="0 separate merge kernel, 1 fused epilogue")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))

@@ -48,6 +48,18 @@ struct Ring_fwd_params; /* csrc/ring.h of this repository: the reference's struc
 #define RING_OPT_MERGE_MODE 1
 #define RING_OPT_CAUSAL_SKIP_EXCHANGE 2 /* 1 (default): under a causal mask, do not ship shards nobody will read */
 #define RING_OPT_RECORD_TIMINGS 3       /* 1: record per-step events so ring_ctx_get_timings() works */
+#define RING_OPT_TRANSPORT 4            /* how K/V shards travel between ranks, see below */
+
+/* Transports of the K/V exchange.  Both keep the same schedule (ring_step_plan) and the same double buffer.
+ *   NCCL:      ncclSend/ncclRecv on the exchange stream (what the reference's NCCL prototype does,
+ *              test/ring_attention_with_nccl.cu:153-156).  NCCL's copy kernels occupy SMs next to the block kernel.
+ *   PEER_COPY: each rank pushes its shard into the destination's receive buffer with a device-to-device copy over
+ *              NVLink (copy engines, no SMs); buffers are shared through CUDA IPC and ordered with stream memory
+ *              operations.  Default when the ranks can map each other's memory; NCCL otherwise.
+ * The environment variable RING_TRANSPORT=nccl|peer chooses at context creation; the option switches later
+ * (collectively: all ranks must switch between the same two calls). */
+#define RING_TRANSPORT_NCCL 0
+#define RING_TRANSPORT_PEER_COPY 1
 
 /*
  * Replaces: ring_attention(FPC* q, FPC* k, FPC* v, float* out, int npes, int mype, int* seqlen,
@@ -79,6 +91,7 @@ int ring_get_unique_id(void* id_out);
 int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id);
 int ring_ctx_destroy(RingCtx* ctx);
 int ring_ctx_set_option(RingCtx* ctx, int option, int value);
+int ring_ctx_get_option(RingCtx* ctx, int option, int* value);
 int ring_set_default_ctx(RingCtx* ctx); /* context used by ring_attention(); NULL clears it */
 
 /*

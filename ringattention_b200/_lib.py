@@ -23,6 +23,9 @@ RING_MERGE_FUSED_EPILOGUE = 1
 RING_OPT_MERGE_MODE = 1
 RING_OPT_CAUSAL_SKIP_EXCHANGE = 2
 RING_OPT_RECORD_TIMINGS = 3
+RING_OPT_TRANSPORT = 4
+RING_TRANSPORT_NCCL = 0
+RING_TRANSPORT_PEER_COPY = 1
 RING_STATIC_MAX_ROWS = 65536
 RING_STATIC_MAX_OUT_ELEMS = 4 * 1024 * 1024
 
@@ -53,6 +56,7 @@ SYMBOLS = {
     "ring_ctx_create": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
     "ring_ctx_destroy": (c_int, [c_void_p]),
     "ring_ctx_set_option": (c_int, [c_void_p, c_int, c_int]),
+    "ring_ctx_get_option": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int)]),
     "ring_set_default_ctx": (c_int, [c_void_p]),
     "ring_ctx_create_local": (c_int, [ctypes.POINTER(c_void_p), c_int]),
     "ring_ctx_set_local_shards": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),

@@ -156,6 +156,11 @@ class RingContext:
     def set_option(self, option: int, value: int) -> None:
         check(_lib.load().ring_ctx_set_option(self._h, int(option), int(value)), "ring_ctx_set_option")
 
+    def get_option(self, option: int) -> int:
+        v = ctypes.c_int(0)
+        check(_lib.load().ring_ctx_get_option(self._h, int(option), ctypes.byref(v)), "ring_ctx_get_option")
+        return v.value
+
     def set_default(self) -> None:
         """Make this the context the plain ring_attention() call uses."""
         check(_lib.load().ring_set_default_ctx(self._h), "ring_set_default_ctx")

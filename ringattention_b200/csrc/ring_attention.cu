@@ -64,10 +64,12 @@ struct NcclApi {
     void* handle = nullptr;
     ncclResult_t (*GetUniqueId)(ncclUniqueId*) = nullptr;
     ncclResult_t (*CommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*CommInitRankConfig)(ncclComm_t*, int, ncclUniqueId, int, ncclConfig_t*) = nullptr;
     ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
     ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
     ncclResult_t (*Send)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*Recv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*AllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
     ncclResult_t (*GroupStart)() = nullptr;
     ncclResult_t (*GroupEnd)() = nullptr;
     const char* (*GetErrorString)(ncclResult_t) = nullptr;
@@ -90,10 +92,12 @@ NcclApi& nccl() {
     if (!api.field) return;
         LOAD(GetUniqueId, "ncclGetUniqueId");
         LOAD(CommInitRank, "ncclCommInitRank");
+        LOAD(CommInitRankConfig, "ncclCommInitRankConfig");
         LOAD(CommDestroy, "ncclCommDestroy");
         LOAD(CommAbort, "ncclCommAbort");
         LOAD(Send, "ncclSend");
         LOAD(Recv, "ncclRecv");
+        LOAD(AllGather, "ncclAllGather");
         LOAD(GroupStart, "ncclGroupStart");
         LOAD(GroupEnd, "ncclGroupEnd");
         LOAD(GetErrorString, "ncclGetErrorString");
@@ -176,6 +180,40 @@ int make_tensor_map(CUtensorMap* tm, const void* base, int batch, int heads, int
     if (r != CUDA_SUCCESS) return fail(RING_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
     return RING_OK;
 }
+
+// ------------------------------------------------------------------------------------------ stream memory operations
+// cuStreamWriteValue32 / cuStreamWaitValue32: a 32-bit store / a ">= value" wait executed by the stream's
+// front end, in stream order, without a kernel.  The peer-copy exchange uses them as cross-process flags.
+using StreamValueFn = CUresult (*)(CUstream, CUdeviceptr, cuuint32_t, unsigned int);
+struct StreamMemOps {
+    StreamValueFn write = nullptr;
+    StreamValueFn wait = nullptr;
+};
+
+int stream_mem_ops(StreamMemOps* out) {
+    static StreamMemOps ops;
+    static std::mutex m;
+    std::lock_guard<std::mutex> lock(m);
+    if (!ops.write) {
+        void *pw = nullptr, *pq = nullptr;
+        cudaDriverEntryPointQueryResult q1, q2;
+        RING_CUDA(cudaGetDriverEntryPoint("cuStreamWriteValue32", &pw, cudaEnableDefault, &q1));
+        RING_CUDA(cudaGetDriverEntryPoint("cuStreamWaitValue32", &pq, cudaEnableDefault, &q2));
+        if (q1 != cudaDriverEntryPointSuccess || q2 != cudaDriverEntryPointSuccess || !pw || !pq)
+            return fail(RING_ERR_UNSUPPORTED, "stream memory operations are not available from this driver");
+        ops.write = reinterpret_cast<StreamValueFn>(pw);
+        ops.wait = reinterpret_cast<StreamValueFn>(pq);
+    }
+    *out = ops;
+    return RING_OK;
+}
+
+#define RING_CU(call)                                                                                     \
+    do {                                                                                                  \
+        CUresult r_ = (call);                                                                             \
+        if (r_ != CUDA_SUCCESS)                                                                           \
+            return fail(RING_ERR_CUDA, "%s failed with CUresult %d (%s:%d)", #call, (int)r_, __FILE__, __LINE__); \
+    } while (0)
 
 // ------------------------------------------------------------------------------------------ launchers
 struct BlockLaunch {
@@ -329,7 +367,25 @@ struct RingCtx {
     bool step_exchanged[kMaxWorld] = {};
     const void* local_k[kMaxWorld] = {};
     const void* local_v[kMaxWorld] = {};
+    // ---- peer-copy transport (RING_TRANSPORT_PEER_COPY) ---------------------------------------------------
+    int transport = RING_TRANSPORT_NCCL;
+    bool peer_ready = false;          // flags exported/imported
+    uint32_t* flags = nullptr;        // own flag block: ready[kMaxWorld] then credit[kMaxWorld]
+    uint32_t* peer_flags[kMaxWorld] = {};
+    void* recv_block = nullptr;       // one allocation holding both receive buffers (peer transport)
+    size_t recv_block_half = 0;       // bytes of one receive buffer inside the block
+    void* peer_recv_block[kMaxWorld] = {};
+    size_t peer_recv_half[kMaxWorld] = {};
+    void* xchg_dev = nullptr;         // staging for the handle all-gathers
+    uint32_t call_seq = 0;
+    cudaEvent_t ev_push_done = nullptr;
+    cudaEvent_t ev_call_done = nullptr;  // end of the previous call on whatever stream it used
+    bool have_call_done = false;
 };
+
+constexpr int kFlagReady = 0;
+constexpr int kFlagCredit = kMaxWorld;
+constexpr size_t kXchgBlob = 128;  // bytes exchanged per rank in a handle all-gather
 
 namespace {
 
@@ -338,8 +394,13 @@ RingCtx* g_solo_ctx = nullptr;  // world-1 context created on demand by ring_att
 
 int ctx_common_init(RingCtx* c) {
     RING_CUDA(cudaGetDevice(&c->device));
-    RING_CUDA(cudaStreamCreateWithFlags(&c->comm_stream, cudaStreamNonBlocking));
+    // The exchange stream gets the highest priority: its few CTAs (NCCL's send/recv kernel) must win an SM
+    // as soon as one frees up, instead of queueing behind the block kernel's thousand pending CTAs.
+    int prio_least = 0, prio_greatest = 0;
+    RING_CUDA(cudaDeviceGetStreamPriorityRange(&prio_least, &prio_greatest));
+    RING_CUDA(cudaStreamCreateWithPriority(&c->comm_stream, cudaStreamNonBlocking, prio_greatest));
     RING_CUDA(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    RING_CUDA(cudaEventCreateWithFlags(&c->ev_call_done, cudaEventDisableTiming));
     for (int i = 0; i < c->world; ++i) {
         RING_CUDA(cudaEventCreate(&c->ev_recv_done[i]));
         RING_CUDA(cudaEventCreate(&c->ev_comm_start[i]));
@@ -359,6 +420,114 @@ int grow(void** buf, size_t* cap, size_t need) {
     *cap = 0;
     RING_CUDA(cudaMalloc(buf, need));
     *cap = need;
+    return RING_OK;
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------------------------------ peer-copy transport
+// The K/V exchange without SMs: every rank PUSHES its own K/V shard into the destination's receive
+// buffer with a device-to-device copy over NVLink (copy engines), on its exchange stream.  The receive
+// buffers and a small flag block of every rank are shared with the other processes through CUDA IPC.
+// Cross-process ordering uses stream memory operations on the flag blocks (no kernels, no spinning SMs):
+//   ready[e]  (in the RECEIVER's block)  written by the origin rank of exchange e after its copy:
+//             "the shard for your step e + 1 has landed";
+//   credit[e] (in the SENDER's block)    written by the destination of exchange e:
+//             "my receive buffer e & 1 is free for you" -- at the start of a call for e < 2, after
+//             compute step e - 1 for e >= 2 (that step was the last reader of the buffer).
+// Values are the call sequence number, compared with >=, so flags are never reset.
+namespace {
+
+int allgather_blobs(RingCtx* c, const void* mine, std::vector<char>& all) {
+    NcclApi& n = nccl();
+    all.assign(kXchgBlob * c->world, 0);
+    char* dev = static_cast<char*>(c->xchg_dev);
+    RING_CUDA(cudaMemcpyAsync(dev + kXchgBlob * (c->world + c->rank), mine, kXchgBlob, cudaMemcpyHostToDevice, c->comm_stream));
+    RING_NCCL(n.AllGather(dev + kXchgBlob * (c->world + c->rank), dev, kXchgBlob, ncclInt8, c->comm, c->comm_stream));
+    RING_CUDA(cudaMemcpyAsync(all.data(), dev, kXchgBlob * c->world, cudaMemcpyDeviceToHost, c->comm_stream));
+    RING_CUDA(cudaStreamSynchronize(c->comm_stream));
+    return RING_OK;
+}
+
+struct HandleBlob {
+    cudaIpcMemHandle_t handle;
+    uint64_t half_bytes;
+    uint64_t valid;
+};
+static_assert(sizeof(HandleBlob) <= kXchgBlob, "blob size");
+
+int peer_setup_flags(RingCtx* c) {
+    StreamMemOps ops;
+    int rc = stream_mem_ops(&ops);
+    if (rc) return rc;
+    RING_CUDA(cudaMalloc(&c->xchg_dev, kXchgBlob * 2 * kMaxWorld));
+    RING_CUDA(cudaMalloc(reinterpret_cast<void**>(&c->flags), 2 * kMaxWorld * sizeof(uint32_t)));
+    RING_CUDA(cudaMemset(c->flags, 0, 2 * kMaxWorld * sizeof(uint32_t)));
+    RING_CUDA(cudaEventCreateWithFlags(&c->ev_push_done, cudaEventDisableTiming));
+    HandleBlob mine;
+    std::memset(&mine, 0, sizeof(mine));
+    cudaError_t e = cudaIpcGetMemHandle(&mine.handle, c->flags);
+    mine.valid = (e == cudaSuccess) ? 1 : 0;
+    if (e != cudaSuccess) (void)cudaGetLastError();
+    char blob[kXchgBlob] = {0};
+    std::memcpy(blob, &mine, sizeof(mine));
+    std::vector<char> all;
+    if ((rc = allgather_blobs(c, blob, all))) return rc;
+    bool ok = true;
+    for (int r = 0; r < c->world && ok; ++r) {
+        HandleBlob hb;
+        std::memcpy(&hb, all.data() + kXchgBlob * r, sizeof(hb));
+        if (!hb.valid) { ok = false; break; }
+        if (r == c->rank) { c->peer_flags[r] = c->flags; continue; }
+        void* p = nullptr;
+        e = cudaIpcOpenMemHandle(&p, hb.handle, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) { (void)cudaGetLastError(); ok = false; break; }
+        c->peer_flags[r] = static_cast<uint32_t*>(p);
+    }
+    // every rank must take the same decision: agree through one more all-gather
+    char vote[kXchgBlob] = {0};
+    vote[0] = ok ? 1 : 0;
+    if ((rc = allgather_blobs(c, vote, all))) return rc;
+    for (int r = 0; r < c->world; ++r)
+        if (!all[kXchgBlob * r]) ok = false;
+    c->peer_ready = ok;
+    return RING_OK;
+}
+
+// Collective: every rank of the context calls it in the same ring_attention_fwd() with the same size.
+int peer_grow_recv(RingCtx* c, size_t half_bytes) {
+    if (half_bytes <= c->recv_block_half) return RING_OK;
+    int rc;
+    std::vector<char> all;
+    char blob[kXchgBlob] = {0};
+    RING_CUDA(cudaDeviceSynchronize());
+    for (int r = 0; r < c->world; ++r) {  // drop the mappings of the buffers that are about to be freed
+        if (r != c->rank && c->peer_recv_block[r]) RING_CUDA(cudaIpcCloseMemHandle(c->peer_recv_block[r]));
+        c->peer_recv_block[r] = nullptr;
+    }
+    if ((rc = allgather_blobs(c, blob, all))) return rc;  // barrier: nobody still maps the old buffers
+    if (c->recv_block) RING_CUDA(cudaFree(c->recv_block));
+    c->recv_block = nullptr;
+    c->recv_block_half = 0;
+    RING_CUDA(cudaMalloc(&c->recv_block, 2 * half_bytes));
+    c->recv_block_half = half_bytes;
+    HandleBlob mine;
+    std::memset(&mine, 0, sizeof(mine));
+    RING_CUDA(cudaIpcGetMemHandle(&mine.handle, c->recv_block));
+    mine.half_bytes = half_bytes;
+    mine.valid = 1;
+    std::memcpy(blob, &mine, sizeof(mine));
+    if ((rc = allgather_blobs(c, blob, all))) return rc;
+    for (int r = 0; r < c->world; ++r) {
+        HandleBlob hb;
+        std::memcpy(&hb, all.data() + kXchgBlob * r, sizeof(hb));
+        c->peer_recv_half[r] = hb.half_bytes;
+        if (r == c->rank) { c->peer_recv_block[r] = c->recv_block; continue; }
+        RING_CUDA(cudaIpcOpenMemHandle(&c->peer_recv_block[r], hb.handle, cudaIpcMemLazyEnablePeerAccess));
+    }
+    c->recv[0] = c->recv_block;
+    c->recv[1] = static_cast<char*>(c->recv_block) + half_bytes;
+    c->recv_cap[0] = c->recv_cap[1] = half_bytes;
     return RING_OK;
 }
 
@@ -431,8 +600,18 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     const bool causal = p.causal != 0;
     int rc;
 
-    if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * shard_bytes))) return rc;
-    if (P > 2 && (rc = grow(&c->recv[1], &c->recv_cap[1], 2 * shard_bytes))) return rc;
+    const bool peer = !c->local && P > 1 && c->transport == RING_TRANSPORT_PEER_COPY;
+    StreamMemOps ops;
+    uint32_t seq = 0;
+    if (peer) {
+        if ((rc = stream_mem_ops(&ops))) return rc;
+        if ((rc = peer_grow_recv(c, 2 * shard_bytes))) return rc;
+        seq = ++c->call_seq;
+    } else {
+        if (c->recv_block) return fail(RING_ERR_UNSUPPORTED, "switching from the peer-copy transport back to NCCL is not supported");
+        if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * shard_bytes))) return rc;
+        if (P > 2 && (rc = grow(&c->recv[1], &c->recv_cap[1], 2 * shard_bytes))) return rc;
+    }
     float* lse = static_cast<float*>(p.lse_ptr);
     if (!lse) {
         if ((rc = grow(reinterpret_cast<void**>(&c->lse_own), &c->lse_own_cap, rows * sizeof(float)))) return rc;
@@ -445,13 +624,26 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
 
     // The exchange stream may touch K/V only once the compute stream's earlier work (which may have
     // produced them) is done.
+    if (c->have_call_done) RING_CUDA(cudaStreamWaitEvent(stream, c->ev_call_done, 0));  // callers may change streams
     if (P > 1) {
         RING_CUDA(cudaEventRecord(c->ev_fork, stream));
         RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_fork, 0));
     }
+    if (peer) {
+        // Both receive buffers are free here (their last readers precede this point on `stream`): tell the
+        // origins of the first two exchanges.
+        for (int e = 0; e < 2 && e < P - 1; ++e) {
+            RingStepPlan pe;
+            if ((rc = ring_step_plan(P, r, e, causal ? 1 : 0, c->causal_skip, &pe))) return rc;
+            if (pe.do_recv)
+                RING_CU(ops.write(reinterpret_cast<CUstream>(stream),
+                                  reinterpret_cast<CUdeviceptr>(c->peer_flags[pe.recv_from] + kFlagCredit + e), seq, 0));
+        }
+    }
 
     c->last_steps = P;
     bool have_partial = false;
+    bool prev_do_recv = false;
     for (int s = 0; s < P; ++s) {
         RingStepPlan plan;
         if ((rc = ring_step_plan(P, r, s, causal ? 1 : 0, c->causal_skip, &plan))) return rc;
@@ -464,11 +656,20 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             const int ndst = plan.send_to;    // who gets this rank's shard
             const bool do_recv = plan.do_recv != 0;
             const bool do_send = plan.do_send != 0;
-            if (s >= 2) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
+            if (s >= 2 && !peer) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
             if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_comm_start[s], c->comm_stream));
             char* dst_k = static_cast<char*>(c->recv[plan.recv_buffer]);
             char* dst_v = dst_k + shard_bytes;
-            if (c->local) {
+            if (peer) {
+                if (do_send) {
+                    CUstream cs = reinterpret_cast<CUstream>(c->comm_stream);
+                    RING_CU(ops.wait(cs, reinterpret_cast<CUdeviceptr>(c->flags + kFlagCredit + s), seq, CU_STREAM_WAIT_VALUE_GEQ));
+                    char* remote = static_cast<char*>(c->peer_recv_block[ndst]) + plan.recv_buffer * c->peer_recv_half[ndst];
+                    RING_CUDA(cudaMemcpyAsync(remote, p.k_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                    RING_CUDA(cudaMemcpyAsync(remote + shard_bytes, p.v_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                    RING_CU(ops.write(cs, reinterpret_cast<CUdeviceptr>(c->peer_flags[ndst] + kFlagReady + s), seq, 0));
+                }
+            } else if (c->local) {
                 if (do_recv) {
                     if (!c->local_k[nsrc] || !c->local_v[nsrc])
                         return fail(RING_ERR_INVALID_ARGUMENT, "local shard %d was not registered", nsrc);
@@ -493,7 +694,15 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         }
 
         // ---- compute step s ----------------------------------------------------------------------------
-        if (s >= 1) RING_CUDA(cudaStreamWaitEvent(stream, c->ev_recv_done[s - 1], 0));
+        if (s >= 1) {
+            if (!peer) {
+                RING_CUDA(cudaStreamWaitEvent(stream, c->ev_recv_done[s - 1], 0));
+            } else if (prev_do_recv) {
+                RING_CU(ops.wait(reinterpret_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(c->flags + kFlagReady + (s - 1)), seq,
+                                 CU_STREAM_WAIT_VALUE_GEQ));
+            }
+        }
+        prev_do_recv = plan.do_recv != 0;
         if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_compute_start[s], stream));
         const bool compute = plan.compute != 0;
         c->step_computed[s] = compute;
@@ -528,7 +737,22 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             have_partial = true;
         }
         RING_CUDA(cudaEventRecord(c->ev_compute_done[s], stream));
+        if (peer && s >= 1 && s + 1 <= P - 2) {
+            // step s was the last reader of receive buffer (s - 1) & 1 = (s + 1) & 1: free it for exchange s + 1
+            RingStepPlan pe;
+            if ((rc = ring_step_plan(P, r, s + 1, causal ? 1 : 0, c->causal_skip, &pe))) return rc;
+            if (pe.do_recv)
+                RING_CU(ops.write(reinterpret_cast<CUstream>(stream),
+                                  reinterpret_cast<CUdeviceptr>(c->peer_flags[pe.recv_from] + kFlagCredit + s + 1), seq, 0));
+        }
     }
+    if (peer) {
+        // the call is complete on `stream` only when this rank's own pushes are done (K/V may then be reused)
+        RING_CUDA(cudaEventRecord(c->ev_push_done, c->comm_stream));
+        RING_CUDA(cudaStreamWaitEvent(stream, c->ev_push_done, 0));
+    }
+    RING_CUDA(cudaEventRecord(c->ev_call_done, stream));
+    c->have_call_done = true;
     return RING_OK;
 }
 
@@ -611,10 +835,36 @@ int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id) {
         if (!n.ok) { delete c; return fail(RING_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
         ncclUniqueId id;
         std::memcpy(&id, unique_id, sizeof(id));
-        ncclResult_t r = n.CommInitRank(&c->comm, world, id, rank);
+        // The exchange only has to keep pace with the block kernel (one K/V shard per ring step), not to
+        // saturate NVLink; every CTA NCCL runs is an SM the block kernel does not get.  Cap them
+        // (RING_NCCL_MAX_CTAS, default 16; 0 leaves NCCL's own choice).
+        int max_ctas = 16;
+        if (const char* e = std::getenv("RING_NCCL_MAX_CTAS")) max_ctas = std::atoi(e);
+        ncclResult_t r;
+        if (max_ctas > 0) {
+            ncclConfig_t cfg = NCCL_CONFIG_INITIALIZER;
+            cfg.maxCTAs = max_ctas;
+            cfg.minCTAs = 1;
+            r = n.CommInitRankConfig(&c->comm, world, id, rank, &cfg);
+        } else {
+            r = n.CommInitRank(&c->comm, world, id, rank);
+        }
         if (r != ncclSuccess) {
             delete c;
             return fail(RING_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString(r));
+        }
+        // Peer-copy transport: share the flag blocks now (collective); fall back to NCCL send/recv if the
+        // processes cannot map each other's memory.
+        const char* want = std::getenv("RING_TRANSPORT");
+        const bool force_nccl = want && std::strcmp(want, "nccl") == 0;
+        if (!force_nccl) {
+            rc = peer_setup_flags(c);
+            if (rc) { ring_ctx_destroy(c); return rc; }
+            c->transport = c->peer_ready ? RING_TRANSPORT_PEER_COPY : RING_TRANSPORT_NCCL;
+            if (!c->peer_ready && want && std::strcmp(want, "peer") == 0) {
+                ring_ctx_destroy(c);
+                return fail(RING_ERR_UNSUPPORTED, "RING_TRANSPORT=peer, but the ranks cannot map each other's memory (CUDA IPC)");
+            }
         }
     }
     *ctx = c;
@@ -659,8 +909,26 @@ int ring_ctx_set_option(RingCtx* ctx, int option, int value) {
         case RING_OPT_RECORD_TIMINGS:
             ctx->record_timings = value ? 1 : 0;
             return RING_OK;
+        case RING_OPT_TRANSPORT:
+            if (value != RING_TRANSPORT_NCCL && value != RING_TRANSPORT_PEER_COPY)
+                return fail(RING_ERR_INVALID_ARGUMENT, "bad transport %d", value);
+            if (value == RING_TRANSPORT_PEER_COPY && !ctx->peer_ready)
+                return fail(RING_ERR_UNSUPPORTED, "the peer-copy transport is not available in this context");
+            ctx->transport = value;
+            return RING_OK;
         default:
             return fail(RING_ERR_INVALID_ARGUMENT, "unknown option %d", option);
+    }
+}
+
+int ring_ctx_get_option(RingCtx* ctx, int option, int* value) {
+    if (!ctx || !value) return fail(RING_ERR_INVALID_ARGUMENT, "null argument");
+    switch (option) {
+        case RING_OPT_MERGE_MODE: *value = ctx->merge_mode; return RING_OK;
+        case RING_OPT_CAUSAL_SKIP_EXCHANGE: *value = ctx->causal_skip; return RING_OK;
+        case RING_OPT_RECORD_TIMINGS: *value = ctx->record_timings; return RING_OK;
+        case RING_OPT_TRANSPORT: *value = ctx->transport; return RING_OK;
+        default: return fail(RING_ERR_INVALID_ARGUMENT, "unknown option %d", option);
     }
 }
 
@@ -675,6 +943,16 @@ int ring_ctx_destroy(RingCtx* c) {
         if (c->ev_compute_start[i]) cudaEventDestroy(c->ev_compute_start[i]);
         if (c->ev_compute_done[i]) cudaEventDestroy(c->ev_compute_done[i]);
     }
+    for (int i = 0; i < c->world; ++i) {
+        if (i == c->rank) continue;
+        if (c->peer_recv_block[i]) cudaIpcCloseMemHandle(c->peer_recv_block[i]);
+        if (c->peer_flags[i]) cudaIpcCloseMemHandle(c->peer_flags[i]);
+    }
+    if (c->recv_block) { cudaFree(c->recv_block); c->recv[0] = c->recv[1] = nullptr; }
+    if (c->flags) cudaFree(c->flags);
+    if (c->xchg_dev) cudaFree(c->xchg_dev);
+    if (c->ev_push_done) cudaEventDestroy(c->ev_push_done);
+    if (c->ev_call_done) cudaEventDestroy(c->ev_call_done);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->comm_stream) cudaStreamDestroy(c->comm_stream);
     for (int i = 0; i < 2; ++i)

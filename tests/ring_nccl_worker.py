@@ -33,6 +33,7 @@ def main():
     ap.add_argument("--config", required=True, choices=sorted(CONFIGS))
     ap.add_argument("--merge-mode", type=int, default=1)
     ap.add_argument("--out", default="")
+    ap.add_argument("--transport", default="default", choices=["default", "nccl", "peer"])
     args = ap.parse_args()
 
     import torch
@@ -61,9 +62,12 @@ def main():
     out = torch.full((B, H, Sl, D), float("nan"), device=dev)
     lse = torch.full((B, H, Sl), float("nan"), device=dev)
     ctx = ra.RingContext.from_torch_distributed()
+    if args.transport != "default":
+        ctx.set_option(ra.RING_OPT_TRANSPORT, ra.RING_TRANSPORT_NCCL if args.transport == "nccl" else ra.RING_TRANSPORT_PEER_COPY)
+    transport = "peer" if ctx.get_option(ra.RING_OPT_TRANSPORT) == ra.RING_TRANSPORT_PEER_COPY else "nccl"
     ctx.set_option(ra.RING_OPT_MERGE_MODE, args.merge_mode)
     ctx.set_option(ra.RING_OPT_RECORD_TIMINGS, 1)
-    for _ in range(2):
+    for _ in range(3):
         out.fill_(float("nan")); lse.fill_(float("nan"))
         ctx.forward(q, k, v, out, lse, causal=causal, softmax_scale=scale)
         ctx.synchronize()
@@ -98,7 +102,7 @@ def main():
     ok = bool(mx[0] <= TOL_O_MAXABS and rel <= TOL_O_RELL2 and mx[1] <= TOL_LSE)
     if rank == 0:
         res = {"config": args.config, "world": world, "B": B, "H": H, "S": S, "D": D, "causal": causal,
-               "merge_mode": args.merge_mode, "max_abs_o": float(mx[0]), "rel_l2_o": rel, "max_abs_lse": float(mx[1]),
+               "merge_mode": args.merge_mode, "transport": transport, "max_abs_o": float(mx[0]), "rel_l2_o": rel, "max_abs_lse": float(mx[1]),
                "ok": ok, "rank0_compute_ms": compute_ms, "rank0_comm_ms": comm_ms, "rank0_exposed_ms": exposed_ms,
                "max_rank_compute_ms": float(tmax[0]), "max_rank_exposed_ms": float(tmax[1]),
                "gen_s": t_gen, "oracle_s": t_oracle, "launches": ra.kernel_launch_count()}

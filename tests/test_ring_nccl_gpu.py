@@ -23,12 +23,13 @@ def _free_port():
     return p
 
 
-def _run(world, config, merge_mode, tmp_path, timeout=1500):
-    out = os.path.join(str(tmp_path), f"{config}_{merge_mode}.json")
+def _run(world, config, merge_mode, tmp_path, timeout=1500, transport="default"):
+    out = os.path.join(str(tmp_path), f"{config}_{merge_mode}_{transport}.json")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
-           os.path.join(ROOT, "tests", "ring_nccl_worker.py"), "--config", config, "--merge-mode", str(merge_mode), "--out", out]
+           os.path.join(ROOT, "tests", "ring_nccl_worker.py"), "--config", config, "--merge-mode", str(merge_mode), "--out", out,
+           "--transport", transport]
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     r = json.load(open(out))
@@ -37,11 +38,14 @@ def _run(world, config, merge_mode, tmp_path, timeout=1500):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
 @pytest.mark.parametrize("config,merge_mode", [("small", 1), ("small", 0), ("small_causal", 1)])
-def test_nccl_ring_small(world, config, merge_mode, tmp_path):
+def test_ring_small(world, config, merge_mode, transport, tmp_path):
+    """Both transports of the exchange: NCCL send/recv and copy-engine pushes into IPC-shared buffers."""
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
-    _run(world, config, merge_mode, tmp_path)
+    r = _run(world, config, merge_mode, tmp_path, transport=transport)
+    assert r["transport"] == transport
 
 
 @pytest.mark.parametrize("config,world", [("c2", 2), ("c3", 4), ("c4", 8), ("c5", 8)])
