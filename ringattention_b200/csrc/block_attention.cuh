@@ -11,16 +11,19 @@
 //   * a CTA owns two 128-row Q tiles of one (batch, head) and walks the K/V shard in 128-row blocks;
 //   * one thread issues TMA loads (Q once, then K_j, V_j through a ring of kStages shared-memory
 //     slots, 128-byte swizzle, 64-element boxes);
-//   * one thread issues tcgen05.mma: S_t = Q_t K_j^T (both operands K-major in shared memory) into
-//     TMEM columns [t*128, t*128+128), and O_t += P_t V_j with P_t read from TMEM (fp16 pairs aliased
-//     onto the first 64 columns of S_t) and V_j MN-major from shared memory, so V is never transposed
-//     (the reference needs ldmatrix.trans for that, csrc/kernel_traits.h:39,93-103);
-//   * two softmax warpgroups (one per Q tile, one thread per row = one TMEM lane) read S with
-//     tcgen05.ld, keep the running max / sum in registers, write P with tcgen05.st and rescale O in
-//     TMEM only when a row maximum grew by more than 2^8 (the stale maximum is exact algebra: it
-//     cancels in O / l and in the LSE);
-//   * the two tiles ping-pong: while one warpgroup does softmax on S_t the tensor pipe runs the other
-//     tile's MMAs.
+//   * one thread PER Q TILE issues tcgen05.mma.  S_t = Q_t K_j^T (both operands K-major in shared
+//     memory) goes to TMEM columns [t*128, t*128+128) in two halves of 64 key columns; O_t += P_t V_j
+//     reads P_t from TMEM (16-bit pairs stored over the UPPER half of S_t) and V_j MN-major from shared
+//     memory, so V is never transposed (the reference needs ldmatrix.trans, csrc/kernel_traits.h:39,93-103)
+//     and the PV product costs no shared-memory bandwidth for its A operand;
+//   * two softmax warpgroups (one per Q tile, one thread per row = one TMEM lane).  A warpgroup reads the
+//     LOWER half of S_t(j) and hands those columns back at once, so the lower half of S_t(j+1) is computed
+//     while softmax(j) runs; the upper half follows the PV product in the issuer's queue.  The next block's
+//     lower half is therefore ready when softmax(j) ends and its upper half arrives while the lower half is
+//     being exponentiated: the serial chain per tile is softmax -> softmax, not softmax -> PV -> QK^T.
+//     Running max / sum live in registers; a new maximum is adopted only when it exceeds the one in use by
+//     more than 2^8 (the stale maximum is exact algebra: it cancels in O / l and in the LSE), in which case
+//     the probabilities already computed, the running sum and O (in TMEM) are rescaled;
 // Every mbarrier wait is bounded (ptx::mbar_wait); on expiry the CTA records a status code, all roles
 // fall through to the common exit and TMEM is released.
 #pragma once
@@ -41,6 +44,7 @@ enum DeviceStatus : int {
     kDevMmaWaitQ = 111,
     kDevMmaWaitKV = 112,
     kDevMmaWaitP = 113,
+    kDevMmaWaitS = 114,
     kDevSoftmaxWaitS = 121,
     kDevSoftmaxWaitO = 122,
 };
@@ -59,9 +63,28 @@ struct BlockFwdArgs {
     int diag;         // (global index of Q row 0) - (global index of K row 0)
     int merge;        // 0: overwrite o/lse; 1: o/lse already hold a partial of the same rows, fold into it
     int* status;      // device status word
+#ifdef RING_TRACE
+    long long* trace;  // debug builds only: clock64 stamps of CTA (0,0), 16 slots per K/V block
+#endif
 };
 
+#ifdef RING_TRACE
+#define RING_TRACE_STAMP(cond, slot) do { if ((cond) && a.trace && blockIdx.x == 0 && blockIdx.y == 0) a.trace[j * 16 + (slot)] = clock64(); } while (0)
+#else
+#define RING_TRACE_STAMP(cond, slot) do { } while (0)
+#endif
+
 constexpr float kRescaleThresholdLog2 = 8.0f;
+
+#ifndef RING_USE_MAX3
+#define RING_USE_MAX3 1  // three-input max.f32 in the row-maximum reductions
+#endif
+#ifndef RING_STAGGER_NS
+#define RING_STAGGER_NS 0  // one-time start delay of the second softmax warpgroup (de-phases the two tiles)
+#endif
+#ifndef RING_POLY_EVERY
+#define RING_POLY_EVERY 0  // N > 0: every N-th exponential is evaluated on the FMA pipe instead of the MUFU
+#endif
 
 template <class T>
 __global__ void __launch_bounds__(T::kNThreads, 1)
@@ -73,7 +96,8 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     constexpr int kTileBytes = T::kTileBytes;
     constexpr int kBoxBytes = T::kBoxBytes;
     constexpr int kBoxes = T::kBoxesPerTile;
-    constexpr uint32_t kIdescQK = umma_idesc_f16(128, T::kBlockN, false, false, T::kIsBf16);
+    constexpr int kHalfN = T::kBlockN / 2;  // key columns per S half
+    constexpr uint32_t kIdescQK = umma_idesc_f16(128, kHalfN, false, false, T::kIsBf16);
     constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, false, true, T::kIsBf16);
 
     extern __shared__ uint8_t smem_raw[];
@@ -89,9 +113,11 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     auto bar_q_full = [&](int t) { return bar0 + 8u * t; };
     auto bar_kv_full = [&](int s) { return bar0 + 8u * (2 + s); };
     auto bar_kv_empty = [&](int s) { return bar0 + 8u * (2 + kStages + s); };
-    auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * kStages + t); };
-    auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kStages + t); };
-    auto bar_o_done = [&](int t) { return bar0 + 8u * (6 + 2 * kStages + t); };
+    auto bar_s_lo_full = [&](int t) { return bar0 + 8u * (2 + 2 * kStages + t); };
+    auto bar_s_hi_full = [&](int t) { return bar0 + 8u * (4 + 2 * kStages + t); };
+    auto bar_s_lo_free = [&](int t) { return bar0 + 8u * (6 + 2 * kStages + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8u * (8 + 2 * kStages + t); };
+    auto bar_o_done = [&](int t) { return bar0 + 8u * (10 + 2 * kStages + t); };
     auto smem_q = [&](int t) { return base + static_cast<uint32_t>(t * kTileBytes); };
     auto smem_kv = [&](int s) { return base + static_cast<uint32_t>((T::kQTiles + s) * kTileBytes); };
 
@@ -99,18 +125,24 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
+    const int r0 = blockIdx.x * T::kBlockM;  // first Q row of this CTA
+    const bool tile1_valid = (r0 + 128) < a.sq;
+    const int ntiles = tile1_valid ? 2 : 1;
+
     if (tid == 0) {
         *abort_flag = 0;
         *prior_error = *reinterpret_cast<volatile int*>(a.status);
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_q_full(t), 1);
-            mbar_init(bar_s_full(t), 1);
-            mbar_init(bar_p_full(t), 128);
+            mbar_init(bar_s_lo_full(t), 1);
+            mbar_init(bar_s_hi_full(t), 1);
+            mbar_init(bar_s_lo_free(t), 4);  // one arrival per softmax warp
+            mbar_init(bar_p_full(t), 4);
             mbar_init(bar_o_done(t), 1);
         }
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar_kv_full(s), 1);
-            mbar_init(bar_kv_empty(s), 1);
+            mbar_init(bar_kv_empty(s), ntiles);  // one tcgen05.commit per Q tile that consumed the slot
         }
         fence_mbar_init();
     }
@@ -135,8 +167,6 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int bh = blockIdx.y;
     const int b = bh / a.heads;
     const int h = bh - b * a.heads;
-    const int r0 = blockIdx.x * T::kBlockM;           // first Q row of this CTA
-    const bool tile1_valid = (r0 + 128) < a.sq;
     int nblk = (a.sk + T::kBlockN - 1) / T::kBlockN;  // K/V blocks to visit
     if (a.causal) {
         const int last_row = min(r0 + T::kBlockM, a.sq) - 1;
@@ -179,189 +209,243 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             }
         }
         __syncwarp();
-    } else if (warp == T::kMmaWarp) {
-        // ======================================================================= UMMA issuer
-        if (lane == 0 && nblk > 0) {
-            int slot = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            auto advance = [&]() { if (++slot == kStages) { slot = 0; phase ^= 1; } };
-            // S_t = Q_t K^T : D/16 instructions of 128 x 128 x 16
-            auto issue_qk = [&](int t, int kslot) {
+    } else if (warp == T::kMmaWarp || warp == T::kMmaWarp + 1) {
+        // ======================================================================= UMMA issuers (one per Q tile)
+        const int t = warp - T::kMmaWarp;
+        if (lane == 0 && nblk > 0 && t < ntiles) {
+            const uint32_t t_s = tmem_base + T::kTmemS0 + t * T::kBlockN;
+            // One half of S_t = Q_t K^T: D/16 instructions of 128 x 64 x 16 against key rows [64 half, 64 half + 64)
+            auto issue_qk_half = [&](int kslot, int half) {
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-                    umma_ss(tmem_base + T::kTmemS0 + t * T::kBlockN, umma_desc_kmajor_sw128(smem_q(t) + off),
-                            umma_desc_kmajor_sw128(smem_kv(kslot) + off), kIdescQK, kk > 0 ? 1u : 0u);
+                    umma_ss(t_s + half * kHalfN, umma_desc_kmajor_sw128(smem_q(t) + off),
+                            umma_desc_kmajor_sw128(smem_kv(kslot) + half * (kHalfN * 128) + off), kIdescQK,
+                            kk > 0 ? 1u : 0u);
                 }
             };
-            // O_t (+)= P_t V : kBlockN/16 instructions of 128 x D x 16, A = fp16 P in TMEM
-            auto issue_pv = [&](int t, int vslot, bool accumulate) {
+            // O_t (+)= P_t V : kBlockN/16 instructions of 128 x D x 16, A = 16-bit P in TMEM, B = V MN-major
+            auto issue_pv = [&](int vslot, bool accumulate) {
 #pragma unroll
                 for (int kk = 0; kk < T::kBlockN / 16; ++kk) {
-                    umma_ts(tmem_base + T::kTmemO0 + t * D, tmem_base + T::kTmemS0 + t * T::kBlockN + kk * 8,
+                    umma_ts(tmem_base + T::kTmemO0 + t * D, t_s + T::kTmemPOffset + kk * 8,
                             umma_desc_mnmajor_sw128(smem_kv(vslot) + kk * 16 * 128, kBoxBytes), kIdescPV,
                             (accumulate || kk > 0) ? 1u : 0u);
                 }
             };
+            // K_j is load number 2j of the ring, V_j load number 2j + 1
+            auto ring_slot = [&](int idx) { return idx % kStages; };
+            auto ring_phase = [&](int idx) { return static_cast<uint32_t>((idx / kStages) & 1); };
 
-            // prologue: S_t(0) for both tiles
-            ok = mbar_wait(bar_q_full(0), 0, abort_flag, a.status, kDevMmaWaitQ) &&
-                 mbar_wait(bar_kv_full(slot), phase, abort_flag, a.status, kDevMmaWaitKV);
+            // S_t(0), both halves
+            bool ok = mbar_wait(bar_q_full(t), 0, abort_flag, a.status, kDevMmaWaitQ) &&
+                      mbar_wait(bar_kv_full(ring_slot(0)), ring_phase(0), abort_flag, a.status, kDevMmaWaitKV);
             if (ok) {
                 tcgen05_fence_after_thread_sync();
-                issue_qk(0, slot);
-                umma_commit(bar_s_full(0));
-                if (tile1_valid) {
-                    ok = mbar_wait(bar_q_full(1), 0, abort_flag, a.status, kDevMmaWaitQ);
-                    if (ok) {
-                        tcgen05_fence_after_thread_sync();
-                        issue_qk(1, slot);
-                        umma_commit(bar_s_full(1));
-                    }
-                }
-                umma_commit(bar_kv_empty(slot));
-                advance();
+                issue_qk_half(ring_slot(0), 0);
+                umma_commit(bar_s_lo_full(t));
+                issue_qk_half(ring_slot(0), 1);
+                umma_commit(bar_s_hi_full(t));
+                umma_commit(bar_kv_empty(ring_slot(0)));
             }
 #pragma unroll 1
             for (int j = 0; j < nblk && ok; ++j) {
                 const bool has_next = (j + 1) < nblk;
-                const uint32_t pj = j & 1;
-                const int vslot = slot;
-                const uint32_t vphase = phase;
-                advance();
-                const int kslot = slot;
-                const uint32_t kphase = phase;
-                if (has_next) advance();
-
-                ok = mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV) &&
-                     mbar_wait(bar_p_full(0), pj, abort_flag, a.status, kDevMmaWaitP);
+                const int kidx = 2 * (j + 1);
+                // lower half of S_t(j + 1): as soon as the warpgroup holds the lower half of S_t(j) in registers
+                if (has_next) {
+                    ok = mbar_wait(bar_s_lo_free(t), j & 1, abort_flag, a.status, kDevMmaWaitS) &&
+                         mbar_wait(bar_kv_full(ring_slot(kidx)), ring_phase(kidx), abort_flag, a.status, kDevMmaWaitKV);
+                    if (!ok) break;
+                    tcgen05_fence_after_thread_sync();
+                    issue_qk_half(ring_slot(kidx), 0);
+                    umma_commit(bar_s_lo_full(t));
+                }
+                // O_t += P_t(j) V_j, then the upper half of S_t(j + 1) over the columns P_t(j) occupied
+                // (the tensor pipe executes one issuer's instructions in order)
+                const int vidx = 2 * j + 1;
+                ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
+                     mbar_wait(bar_kv_full(ring_slot(vidx)), ring_phase(vidx), abort_flag, a.status, kDevMmaWaitKV);
                 if (!ok) break;
+                RING_TRACE_STAMP(true, 6 + t);
                 tcgen05_fence_after_thread_sync();
-                issue_pv(0, vslot, j > 0);
-                umma_commit(bar_o_done(0));
+                issue_pv(ring_slot(vidx), j > 0);
+                umma_commit(bar_o_done(t));
+                umma_commit(bar_kv_empty(ring_slot(vidx)));
                 if (has_next) {
-                    ok = mbar_wait(bar_kv_full(kslot), kphase, abort_flag, a.status, kDevMmaWaitKV);
-                    if (!ok) break;
-                    tcgen05_fence_after_thread_sync();
-                    issue_qk(0, kslot);
-                    umma_commit(bar_s_full(0));
-                }
-                if (tile1_valid) {
-                    ok = mbar_wait(bar_p_full(1), pj, abort_flag, a.status, kDevMmaWaitP);
-                    if (!ok) break;
-                    tcgen05_fence_after_thread_sync();
-                    issue_pv(1, vslot, j > 0);
-                    umma_commit(bar_o_done(1));
-                }
-                umma_commit(bar_kv_empty(vslot));
-                if (has_next) {
-                    if (tile1_valid) {
-                        issue_qk(1, kslot);
-                        umma_commit(bar_s_full(1));
-                    }
-                    umma_commit(bar_kv_empty(kslot));
+                    issue_qk_half(ring_slot(kidx), 1);
+                    umma_commit(bar_s_hi_full(t));
+                    umma_commit(bar_kv_empty(ring_slot(kidx)));
                 }
             }
         }
         __syncwarp();
-    } else {
+    } else if (warp < T::kSoftmaxWarps) {
         // ======================================================================= softmax warpgroups
         const int t = warp >> 2;  // Q tile of this warpgroup
         const int quarter = warp & 3;
-        if (t == 0 || tile1_valid) {
+        if (t < ntiles) {
             const int row = r0 + t * 128 + quarter * 32 + lane;  // row of the Q shard == TMEM lane
             const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
             const uint32_t t_s = tmem_base + lane_addr + T::kTmemS0 + t * T::kBlockN;
+            const uint32_t t_p = t_s + T::kTmemPOffset;
             const uint32_t t_o = tmem_base + lane_addr + T::kTmemO0 + t * D;
             const float c = a.scale_log2;
 
             float m_run = -INFINITY;  // maximum the exponentials are currently taken against (raw score)
             float l_run = 0.f;        // running sum of exp2((s - m_run) c), from unrounded fp32 p
             bool ok = true;
+#if RING_STAGGER_NS > 0
+            if (t == 1) __nanosleep(RING_STAGGER_NS);
+#endif
+
+            auto max64 = [&](const float* s) -> float {
+#if RING_USE_MAX3
+                float mx0 = fmax3(s[0], s[1], s[2]), mx1 = fmax3(s[3], s[4], s[5]);
+#pragma unroll
+                for (int i = 6; i + 3 < 64; i += 4) {
+                    mx0 = fmax3(mx0, s[i], s[i + 1]);
+                    mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
+                }
+                return fmax3(mx0, mx1, fmaxf(s[62], s[63]));
+#else
+                float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+                for (int i = 4; i < 64; i += 4) {
+                    mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]);
+                    mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]);
+                }
+                return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+#endif
+            };
+            // s[i] <- exp2(s[i] c - ms) in place (fp32, unrounded); returns the sum
+            auto exp64 = [&](float* s, float ms) -> float {
+                const float nms = -ms;
+                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const float x = fmaf(s[i + u], c, nms);
+#if RING_POLY_EVERY > 0
+                        s[i + u] = ((i + u) % RING_POLY_EVERY == RING_POLY_EVERY - 1) ? ex2_poly(x) : ex2_approx(x);
+#else
+                        s[i + u] = ex2_approx(x);
+#endif
+                    }
+                    a0 += s[i]; a1 += s[i + 1]; a2 += s[i + 2]; a3 += s[i + 3];
+                }
+                return (a0 + a1) + (a2 + a3);
+            };
+
+            auto pack64 = [&](const float* s, uint32_t (&pk)[32]) {
+#pragma unroll
+                for (int x = 0; x < 32; ++x)
+                    pk[x] = T::kIsBf16 ? pack_bf16x2(s[2 * x], s[2 * x + 1]) : pack_f16x2(s[2 * x], s[2 * x + 1]);
+            };
 
 #pragma unroll 1
             for (int j = 0; j < nblk; ++j) {
-                ok = mbar_wait(bar_s_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tcgen05_fence_after_thread_sync();
-
-                uint32_t sr[128];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    tmem_ld_x32(t_s + 32 * i, *reinterpret_cast<uint32_t(*)[32]>(&sr[32 * i]));
-                tmem_wait_ld();
+                uint32_t sr[64];   // one half of the S row, then its probabilities (fp32, in place)
+                uint32_t plo[32];  // lower half of P_t(j) as 16-bit pairs, held until the upper half of S is out of TMEM
                 float* s = reinterpret_cast<float*>(sr);
-
                 // masking: only blocks that straddle the causal diagonal or the end of the shard
                 const int col0 = j * T::kBlockN;
                 int limit = a.sk - col0;                                  // valid columns of this block
                 if (a.causal) limit = min(limit, row + a.diag - col0 + 1);  // visible columns of this row
                 const bool masked_block = (a.sk - col0 < T::kBlockN) ||
                                           (a.causal && (r0 + t * 128 + a.diag - col0 + 1) < T::kBlockN);
+                float alpha_tot = 1.f;  // factor owed to everything accumulated before this block
+
+                // ---------------- lower half: key columns [0, 64) of the block
+                ok = mbar_wait(bar_s_lo_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 0);
+                tcgen05_fence_after_thread_sync();
+                tmem_ld_x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+                tmem_ld_x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+                tmem_wait_ld();
+                // those columns are in registers: hand them back so the lower half of S_t(j + 1) is computed meanwhile
+                tcgen05_fence_before_thread_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_s_lo_free(t));
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 1);
                 if (masked_block) {
 #pragma unroll
-                    for (int cidx = 0; cidx < 128; ++cidx)
-                        if (cidx >= limit) s[cidx] = -INFINITY;
+                    for (int i = 0; i < 64; ++i)
+                        if (i >= limit) s[i] = -INFINITY;
                 }
-
-                float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
-#pragma unroll
-                for (int cidx = 4; cidx < 128; cidx += 4) {
-                    mx0 = fmaxf(mx0, s[cidx]);
-                    mx1 = fmaxf(mx1, s[cidx + 1]);
-                    mx2 = fmaxf(mx2, s[cidx + 2]);
-                    mx3 = fmaxf(mx3, s[cidx + 3]);
-                }
-                const float m_new = fmaxf(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)), m_run);
-
-                // Lazy rescale: adopt the new maximum only when it exceeds the one in use by more than
-                // 2^8 in the exponent (or nothing is in use yet).  Warp-uniform, because rescaling O
-                // is a warp-collective TMEM round trip.
-                const bool need = (m_new > m_run) && ((m_run == -INFINITY) || ((m_new - m_run) * c > kRescaleThresholdLog2));
-                if (__any_sync(0xffffffffu, need)) {
-                    const float alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - m_new) * c);
-                    l_run *= alpha;
-                    if (j > 0) {
-                        ok = mbar_wait(bar_o_done(t), (j - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (!ok) break;
-                        tcgen05_fence_after_thread_sync();
-#pragma unroll
-                        for (int i = 0; i < D / 32; ++i) {
-                            uint32_t orr[32];
-                            tmem_ld_x32(t_o + 32 * i, orr);
-                            tmem_wait_ld();
-#pragma unroll
-                            for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha);
-                            tmem_st_x32(t_o + 32 * i, orr);
-                        }
+                {
+                    const float mx = max64(s);
+                    if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * c > kRescaleThresholdLog2)) {
+                        alpha_tot = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - mx) * c);
+                        m_run = mx;
                     }
-                    m_run = m_new;
+                }
+                float ms = (m_run == -INFINITY) ? 0.f : m_run * c;
+                float l_blk = exp64(s, ms);
+                pack64(s, plo);
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 2);
+
+                // ---------------- upper half: key columns [64, 128); it is written after P_t(j - 1) was consumed
+                ok = mbar_wait(bar_s_hi_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                tcgen05_fence_after_thread_sync();
+                tmem_ld_x32(t_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
+                tmem_ld_x32(t_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
+                tmem_wait_ld();
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 3);
+                if (masked_block) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (64 + i >= limit) s[i] = -INFINITY;
+                }
+                {
+                    const float mx = max64(s);
+                    if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * c > kRescaleThresholdLog2)) {
+                        // the lower half was taken against the old maximum: bring it to the new one
+                        const float al = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - mx) * c);
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) plo[x] = T::kIsBf16 ? scale_bf16x2(plo[x], al) : scale_f16x2(plo[x], al);
+                        l_blk *= al;
+                        alpha_tot *= al;
+                        m_run = mx;
+                        ms = m_run * c;
+                    }
+                }
+                l_blk += exp64(s, ms);
+                l_run = fmaf(l_run, alpha_tot, l_blk);
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 5);
+
+                // O_t is rescaled only when some row of the warp adopted a new maximum (a warp-collective TMEM
+                // round trip).  S_hi(j) complete implies P_t(j - 1) V is complete: nothing of this tile is in flight.
+                if (j > 0 && __any_sync(0xffffffffu, alpha_tot != 1.f)) {
+#pragma unroll
+                    for (int i = 0; i < D / 32; ++i) {
+                        uint32_t orr[32];
+                        tmem_ld_x32(t_o + 32 * i, orr);
+                        tmem_wait_ld();
+#pragma unroll
+                        for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha_tot);
+                        tmem_st_x32(t_o + 32 * i, orr);
+                    }
                 }
 
-                const float ms = (m_run == -INFINITY) ? 0.f : m_run * c;
-                float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int x = 0; x < 16; x += 2) {
-                        const float p0 = ex2_approx(fmaf(s[32 * i + 2 * x + 0], c, -ms));
-                        const float p1 = ex2_approx(fmaf(s[32 * i + 2 * x + 1], c, -ms));
-                        const float p2 = ex2_approx(fmaf(s[32 * i + 2 * x + 2], c, -ms));
-                        const float p3 = ex2_approx(fmaf(s[32 * i + 2 * x + 3], c, -ms));
-                        l0 += p0; l1 += p1; l2 += p2; l3 += p3;
-                        pk[x] = T::kIsBf16 ? pack_bf16x2(p0, p1) : pack_f16x2(p0, p1);
-                        pk[x + 1] = T::kIsBf16 ? pack_bf16x2(p2, p3) : pack_f16x2(p2, p3);
-                    }
-                    tmem_st_x16(t_s + 16 * i, pk);  // 32 probabilities = 16 packed columns
+                // P_t(j): 128 probabilities -> 64 packed columns over the upper half of S_t
+                tmem_st_x32(t_p, plo);
+                {
+                    uint32_t phi[32];
+                    pack64(s, phi);
+                    tmem_st_x32(t_p + 32, phi);
                 }
-                l_run += (l0 + l1) + (l2 + l3);
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, 14 + t);
                 tmem_wait_st();
                 tcgen05_fence_before_thread_sync();
-                mbar_arrive(bar_p_full(t));
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_p_full(t));  // one arrival per warp (barrier count 4)
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 4);
             }
 
             // ---- epilogue: O / l, LSE, optional fold into an earlier partial -----------------------

@@ -51,23 +51,25 @@ struct Ring_fwd_traits : public Base
     // ---- warp roles -----------------------------------------------------------------------
     static constexpr int kQTiles = kBlockM / Base::kUmmaM;       // 2: ping-pong pair
     static constexpr int kSoftmaxWarps = 4 * kQTiles;            // one warpgroup per Q tile, 1 thread = 1 row
-    static constexpr int kMmaWarp = kSoftmaxWarps;               // single-thread UMMA issue
-    static constexpr int kLoadWarp = kSoftmaxWarps + 1;          // single-thread TMA issue
-    static_assert(kNWarps == kSoftmaxWarps + 2, "8 softmax warps + MMA warp + load warp");
+    static constexpr int kMmaWarp = kSoftmaxWarps;               // warps 8, 9: single-thread UMMA issue for Q tile 0, 1
+    static constexpr int kLoadWarp = kSoftmaxWarps + kQTiles;    // warp 10: single-thread TMA issue (warp 11 idles)
+    static_assert(kNWarps == kSoftmaxWarps + 4, "8 softmax warps + one producer warpgroup (2 MMA, 1 load, 1 spare)");
+
 
     // ---- shared memory ----------------------------------------------------------------------
     static constexpr int kBoxesPerTile = kHeadDim / Base::kSwizzleElems;       // TMA boxes per 128-row tile
     static constexpr int kBoxBytes = 128 * Base::kSwizzleElems * 2;            // 16 KiB
     static constexpr int kTileBytes = kBoxesPerTile * kBoxBytes;               // one 128 x kHeadDim tile
     static constexpr int kStages = kHeadDim == 128 ? 5 : 8;                    // K/V ring slots (K and V alternate)
-    static constexpr int kNumBarriers = 2 /*q_full*/ + 2 * kStages + 3 * kQTiles /*s_full,p_full,o_done*/;
+    static constexpr int kNumBarriers = 2 /*q_full*/ + 2 * kStages + 5 * kQTiles /*s_lo_full,s_hi_full,s_lo_free,p_full,o_done*/;
     static constexpr int kSmemTiles = (kQTiles + kStages) * kTileBytes;
     static constexpr int kSmemSize = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers, TMEM slot, flags*/;
     static_assert(kSmemSize <= 227 * 1024, "exceeds the 227 KiB per-CTA limit");
 
     // ---- tensor memory (512 columns x 128 lanes x 32 bit) ------------------------------------------
     static constexpr int kTmemCols = 512;
-    static constexpr int kTmemS0 = 0;                 // S tile t at columns t*128; fp16 P aliases its first 64
+    static constexpr int kTmemS0 = 0;                 // S tile t at columns t*128; 16-bit P aliases its UPPER 64 columns
+    static constexpr int kTmemPOffset = kBlockN / 2;  // so that the lower half of the next S can be written early
     static constexpr int kTmemO0 = kQTiles * kBlockN; // O tile t at kTmemO0 + t*kHeadDim
     static_assert(kTmemO0 + kQTiles * kHeadDim <= kTmemCols, "TMEM budget");
 };

@@ -51,6 +51,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// Non-blocking test of a phase (used by the UMMA issuer to serve whichever tile is ready first).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Makes this thread's earlier generic-proxy writes to shared memory visible to the async proxy
+// (tcgen05.mma / TMA reads of shared memory).
+__device__ __forceinline__ void fence_proxy_async_shared() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+
 // Every wait in the kernels is bounded.  A wait that does not complete within kWaitLimitNs
 // raises the CTA-wide abort flag (shared memory), records `code` in the global status word and
 // returns false; every other wait of the CTA sees the flag within a few hundred polls and
@@ -219,11 +242,80 @@ __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// Packed 16-bit pair times a broadcast fp32 factor (factor rounded to the pair's format).
+__device__ __forceinline__ uint32_t scale_f16x2(uint32_t v, float f) {
+    uint32_t ff, r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %1;" : "=r"(ff) : "f"(f));
+    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(ff));
+    return r;
+}
+__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t v, float f) {
+    uint32_t ff, r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(ff) : "f"(f));
+    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(ff));
+    return r;
+}
+
+// Register reallocation between warpgroups (all four warps of the warpgroup must execute it).
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_inc() {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+template <int kRegs>
+__device__ __forceinline__ void setmaxnreg_dec() {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegs));
+}
+
 // ---------------------------------------------------------------- small math
+// Packed fp32 pairs (sm_100): one instruction, two lanes.  Operands are passed as scalars and paired
+// inside the asm block so that nothing has to be addressable (no local-memory round trip).
+__device__ __forceinline__ void ffma2(float& d0, float& d1, float a0, float a1, float b0, float b1, float c0, float c1) {
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rc, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "mov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+__device__ __forceinline__ void fadd2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "add.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 2^x on the FMA pipe (no MUFU): x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-4
+// minimax polynomial (relative error < 2.7e-6), 2^n by adding n to the exponent field.
+// Inputs below -125 are clamped (the result, 2^-125, is zero for every purpose here); x must be < 128.
+__device__ __forceinline__ float ex2_poly(float x) {
+    const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds x to the nearest integer in the low mantissa bits
+    x = fmaxf(x, -125.f);
+    const float r = x + kMagic;
+    const float f = x - (r - kMagic);
+    float p = 9.570101276e-03f;
+    p = fmaf(p, f, 5.591785908e-02f);
+    p = fmaf(p, f, 2.402474433e-01f);
+    p = fmaf(p, f, 6.931217909e-01f);
+    p = fmaf(p, f, 9.999992847e-01f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     uint32_t r;

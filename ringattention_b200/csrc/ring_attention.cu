@@ -56,6 +56,9 @@ int fail(int code, const char* fmt, ...) {
     } while (0)
 
 std::atomic<int64_t> g_launches{0};
+#ifdef RING_TRACE
+long long* g_trace = nullptr;  // debug builds only
+#endif
 
 // ------------------------------------------------------------------------------------------ NCCL (loaded lazily)
 // The library is usable on one GPU without NCCL being present; multi-rank contexts load it on demand.
@@ -262,6 +265,9 @@ int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t st
     a.diag = static_cast<int>(diag);
     a.merge = L.merge ? 1 : 0;
     a.status = st->d_status;
+#ifdef RING_TRACE
+    a.trace = g_trace;
+#endif
 
     dim3 grid((L.sq + Traits::kBlockM - 1) / Traits::kBlockM, L.batch * L.heads);
     dim3 block(Traits::kNThreads);
@@ -289,18 +295,18 @@ int validate_block(const BlockLaunch& L) {
 }
 
 // Shape dispatch: the reference instantiates Ring_fwd_traits<64, 64, 64, 4, half> only
-// (csrc/ring_attention.cu:707-716); here <64|128, 256, 128, 10, half|bf16>.
+// (csrc/ring_attention.cu:707-716); here <64|128, 256, 128, 12, half|bf16>.
 int launch_block(const BlockLaunch& L, cudaStream_t stream) {
     int rc = validate_block(L);
     if (rc) return rc;
     DeviceState* st = nullptr;
     if ((rc = device_state(&st))) return rc;
     if (L.dim == 128) {
-        if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 10, __nv_bfloat16>>(L, st, stream);
-        return launch_block_instance<Ring_fwd_traits<128, 256, 128, 10, __half>>(L, st, stream);
+        if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(L, st, stream);
+        return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __half>>(L, st, stream);
     }
-    if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<64, 256, 128, 10, __nv_bfloat16>>(L, st, stream);
-    return launch_block_instance<Ring_fwd_traits<64, 256, 128, 10, __half>>(L, st, stream);
+    if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<64, 256, 128, 12, __nv_bfloat16>>(L, st, stream);
+    return launch_block_instance<Ring_fwd_traits<64, 256, 128, 12, __half>>(L, st, stream);
 }
 
 int launch_merge(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part, int64_t rows, int dim,
@@ -1157,6 +1163,9 @@ int launch_block_static(const StaticChunk& c, StaticSetup* s, cudaStream_t strea
     a.diag = static_cast<int>(-c.k_off);
     a.merge = 0;
     a.status = reinterpret_cast<int*>(s->base);  // header word 0
+#ifdef RING_TRACE
+    a.trace = nullptr;
+#endif
     dim3 grid((c.sq + Traits::kBlockM - 1) / Traits::kBlockM, c.batch * c.heads);
     kernel<<<grid, dim3(Traits::kNThreads), Traits::kSmemSize, stream>>>(tq, tk, tv, a);
     RING_CUDA(cudaGetLastError());
@@ -1205,11 +1214,11 @@ extern "C" int ring_attention_chunked_fwd_static(const void* q, const void* k, c
         c.o = c0 == 0 ? o : o_part;
         c.lse = c0 == 0 ? lse : lse_part;
         if (dim == 128) {
-            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<128, 256, 128, 10, __nv_bfloat16>>(c, s, stream)
-                         : launch_block_static<Ring_fwd_traits<128, 256, 128, 10, __half>>(c, s, stream);
+            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(c, s, stream)
+                         : launch_block_static<Ring_fwd_traits<128, 256, 128, 12, __half>>(c, s, stream);
         } else {
-            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<64, 256, 128, 10, __nv_bfloat16>>(c, s, stream)
-                         : launch_block_static<Ring_fwd_traits<64, 256, 128, 10, __half>>(c, s, stream);
+            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<64, 256, 128, 12, __nv_bfloat16>>(c, s, stream)
+                         : launch_block_static<Ring_fwd_traits<64, 256, 128, 12, __half>>(c, s, stream);
         }
         if (rc) return rc;
         if (c0 > 0) {
@@ -1227,3 +1236,7 @@ extern "C" int ring_attention_chunked_fwd_static(const void* q, const void* k, c
     }
     return RING_OK;
 }
+
+#ifdef RING_TRACE
+extern "C" int ring_debug_set_trace(long long* buf) { g_trace = buf; return 0; }
+#endif

@@ -104,11 +104,15 @@ def test_block_causal_offsets(ra, D, offs):
 
 
 def test_large_scores_and_lazy_rescale(ra):
-    """Inputs with gain 3 make row maxima jump by far more than 2^8 between blocks, so the in-TMEM
-    rescale of O runs; gain 0.5 (config 3 of the benchmark list) keeps it idle."""
+    """Q, K with gain 3 make row maxima jump by far more than 2^8 between blocks, so maxima are adopted and O
+    is rescaled in TMEM often; gain 0.5 (config 3 of the benchmark list) leaves that path idle.  V keeps unit
+    gain: P is rounded to fp16 (relative 2^-11), so for a nearly one-hot row the output error is about
+    |v| * 5e-4, and the 2e-3 bound of the path is stated for N(0,1) values."""
     B, H, S, D = 1, 2, 1024, 128
     for gain, scale in ((3.0, 0.5), (0.5, D ** -0.5)):
-        q, k, v = synthetic.make_qkv(55, B, H, D, 0, S, gain)
+        q = synthetic.make_shard("q", 55, B, H, D, 0, S, gain)
+        k = synthetic.make_shard("k", 55, B, H, D, 0, S, gain)
+        v = synthetic.make_shard("v", 55, B, H, D, 0, S, min(gain, 1.0))
         o, lse = _run_block(ra, q, k, v, scale)
         want_o, want_lse = oracle.attention_fwd(q, k, v, scale)
         assert_parity(o, lse, want_o, want_lse, f"gain {gain}")
