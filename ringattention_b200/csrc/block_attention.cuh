@@ -11,19 +11,21 @@
 //   * a CTA owns two 128-row Q tiles of one (batch, head) and walks the K/V shard in 128-row blocks;
 //   * one thread issues TMA loads (Q once, then K_j, V_j through a ring of kStages shared-memory
 //     slots, 128-byte swizzle, 64-element boxes);
-//   * one thread PER Q TILE issues tcgen05.mma.  S_t = Q_t K_j^T (both operands K-major in shared
-//     memory) goes to TMEM columns [t*128, t*128+128) in two halves of 64 key columns; O_t += P_t V_j
-//     reads P_t from TMEM (16-bit pairs stored over the UPPER half of S_t) and V_j MN-major from shared
+//   * one thread issues tcgen05.mma.  S_t = Q_t K_j^T (both operands K-major in shared memory, N = 128:
+//     a narrower N would re-read Q from shared memory, whose ~75 B/clock operand bandwidth is what bounds
+//     these instructions) goes to ONE S buffer of 128 TMEM columns that the two Q tiles use in turn;
+//     O_t += P_t V_j reads P_t from its own 64 TMEM columns (16-bit pairs) and V_j MN-major from shared
 //     memory, so V is never transposed (the reference needs ldmatrix.trans, csrc/kernel_traits.h:39,93-103)
-//     and the PV product costs no shared-memory bandwidth for its A operand;
-//   * two softmax warpgroups (one per Q tile, one thread per row = one TMEM lane).  A warpgroup reads the
-//     LOWER half of S_t(j) and hands those columns back at once, so the lower half of S_t(j+1) is computed
-//     while softmax(j) runs; the upper half follows the PV product in the issuer's queue.  The next block's
-//     lower half is therefore ready when softmax(j) ends and its upper half arrives while the lower half is
-//     being exponentiated: the serial chain per tile is softmax -> softmax, not softmax -> PV -> QK^T.
-//     Running max / sum live in registers; a new maximum is adopted only when it exceeds the one in use by
-//     more than 2^8 (the stale maximum is exact algebra: it cancels in O / l and in the LSE), in which case
-//     the probabilities already computed, the running sum and O (in TMEM) are rescaled;
+//     and the PV product spends no shared-memory bandwidth on its A operand;
+//   * two softmax warpgroups (one per Q tile, one thread per row = one TMEM lane).  A warpgroup reads its
+//     S_t(j) into registers and hands the S buffer to the other tile at once; because P has columns of its
+//     own, S_t(j+1) is computed while the OTHER tile runs its softmax, and the serial chain per tile is
+//     softmax -> softmax rather than softmax -> PV -> QK^T.  The tiles settle half a period apart, which also
+//     keeps their exponentials from competing for the MUFU all the time.  Running max / sum live in
+//     registers; a new maximum is adopted only when it exceeds the one in use by more than 2^8 (the stale
+//     maximum is exact algebra: it cancels in O / l and in the LSE), and then O is rescaled in TMEM;
+//   * the producer warpgroup gives registers back (setmaxnreg) and the softmax warpgroups take them, so a
+//     whole S row plus its packed probabilities stay in registers without spilling.
 // Every mbarrier wait is bounded (ptx::mbar_wait); on expiry the CTA records a status code, all roles
 // fall through to the common exit and TMEM is released.
 #pragma once
@@ -47,6 +49,7 @@ enum DeviceStatus : int {
     kDevMmaWaitS = 114,
     kDevSoftmaxWaitS = 121,
     kDevSoftmaxWaitO = 122,
+    kDevSoftmaxWaitTurn = 123,
 };
 
 struct BlockFwdArgs {
@@ -64,12 +67,12 @@ struct BlockFwdArgs {
     int merge;        // 0: overwrite o/lse; 1: o/lse already hold a partial of the same rows, fold into it
     int* status;      // device status word
 #ifdef RING_TRACE
-    long long* trace;  // debug builds only: clock64 stamps of CTA (0,0), 16 slots per K/V block
+    long long* trace;  // debug builds only: clock64 stamps of CTA (0,0), 32 slots per K/V block
 #endif
 };
 
 #ifdef RING_TRACE
-#define RING_TRACE_STAMP(cond, slot) do { if ((cond) && a.trace && blockIdx.x == 0 && blockIdx.y == 0) a.trace[j * 16 + (slot)] = clock64(); } while (0)
+#define RING_TRACE_STAMP(cond, slot) do { if ((cond) && a.trace && blockIdx.x == 0 && blockIdx.y == 0) a.trace[j * 32 + (slot)] = clock64(); } while (0)
 #else
 #define RING_TRACE_STAMP(cond, slot) do { } while (0)
 #endif
@@ -77,10 +80,7 @@ struct BlockFwdArgs {
 constexpr float kRescaleThresholdLog2 = 8.0f;
 
 #ifndef RING_USE_MAX3
-#define RING_USE_MAX3 1  // three-input max.f32 in the row-maximum reductions
-#endif
-#ifndef RING_STAGGER_NS
-#define RING_STAGGER_NS 0  // one-time start delay of the second softmax warpgroup (de-phases the two tiles)
+#define RING_USE_MAX3 1  // three-input max.f32 in the row-maximum reduction
 #endif
 #ifndef RING_POLY_EVERY
 #define RING_POLY_EVERY 0  // N > 0: every N-th exponential is evaluated on the FMA pipe instead of the MUFU
@@ -96,8 +96,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     constexpr int kTileBytes = T::kTileBytes;
     constexpr int kBoxBytes = T::kBoxBytes;
     constexpr int kBoxes = T::kBoxesPerTile;
-    constexpr int kHalfN = T::kBlockN / 2;  // key columns per S half
-    constexpr uint32_t kIdescQK = umma_idesc_f16(128, kHalfN, false, false, T::kIsBf16);
+    constexpr uint32_t kIdescQK = umma_idesc_f16(128, T::kBlockN, false, false, T::kIsBf16);
     constexpr uint32_t kIdescPV = umma_idesc_f16(128, D, false, true, T::kIsBf16);
 
     extern __shared__ uint8_t smem_raw[];
@@ -113,11 +112,10 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     auto bar_q_full = [&](int t) { return bar0 + 8u * t; };
     auto bar_kv_full = [&](int s) { return bar0 + 8u * (2 + s); };
     auto bar_kv_empty = [&](int s) { return bar0 + 8u * (2 + kStages + s); };
-    auto bar_s_lo_full = [&](int t) { return bar0 + 8u * (2 + 2 * kStages + t); };
-    auto bar_s_hi_full = [&](int t) { return bar0 + 8u * (4 + 2 * kStages + t); };
-    auto bar_s_lo_free = [&](int t) { return bar0 + 8u * (6 + 2 * kStages + t); };
-    auto bar_p_full = [&](int t) { return bar0 + 8u * (8 + 2 * kStages + t); };
-    auto bar_o_done = [&](int t) { return bar0 + 8u * (10 + 2 * kStages + t); };
+    auto bar_s_full = [&](int t) { return bar0 + 8u * (2 + 2 * kStages + t); };
+    auto bar_p_full = [&](int t) { return bar0 + 8u * (4 + 2 * kStages + t); };
+    auto bar_o_done = [&](int t) { return bar0 + 8u * (6 + 2 * kStages + t); };
+    const uint32_t bar_s_free = bar0 + 8u * (8 + 2 * kStages);  // the shared S buffer has been read out
     auto smem_q = [&](int t) { return base + static_cast<uint32_t>(t * kTileBytes); };
     auto smem_kv = [&](int s) { return base + static_cast<uint32_t>((T::kQTiles + s) * kTileBytes); };
 
@@ -134,12 +132,11 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         *prior_error = *reinterpret_cast<volatile int*>(a.status);
         for (int t = 0; t < 2; ++t) {
             mbar_init(bar_q_full(t), 1);
-            mbar_init(bar_s_lo_full(t), 1);
-            mbar_init(bar_s_hi_full(t), 1);
-            mbar_init(bar_s_lo_free(t), 4);  // one arrival per softmax warp
-            mbar_init(bar_p_full(t), 4);
+            mbar_init(bar_s_full(t), 1);
+            mbar_init(bar_p_full(t), 4);  // one arrival per softmax warp
             mbar_init(bar_o_done(t), 1);
         }
+        mbar_init(bar_s_free, 4);
         for (int s = 0; s < kStages; ++s) {
             mbar_init(bar_kv_full(s), 1);
             mbar_init(bar_kv_empty(s), ntiles);  // one tcgen05.commit per Q tile that consumed the slot
@@ -175,155 +172,201 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         nblk = min(nblk, vis_blk);
     }
 
-    if (warp == T::kLoadWarp) {
-        // ======================================================================= TMA producer
-        if (lane == 0 && nblk > 0) {
-            mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
+    if (warp >= T::kSoftmaxWarps) {
+        // ############################################################## producer warpgroup (warps 8..11)
+        setmaxnreg_dec<T::kProducerRegs>();
+        if (warp == T::kLoadWarp) {
+            // =================================================================== TMA producer
+            if (lane == 0 && nblk > 0) {
+                mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
 #pragma unroll
-            for (int x = 0; x < kBoxes; ++x)
-                tma_load_4d(smem_q(0) + x * kBoxBytes, &tm_q, bar_q_full(0), x * 64, r0, h, b);
-            int slot = 0;
-            uint32_t wrap = 0;  // how many times the ring has wrapped
-            bool ok = true;
+                for (int x = 0; x < kBoxes; ++x)
+                    tma_load_4d(smem_q(0) + x * kBoxBytes, &tm_q, bar_q_full(0), x * 64, r0, h, b);
+                int slot = 0;
+                uint32_t wrap = 0;  // how many times the ring has wrapped
+                bool ok = true;
 #pragma unroll 1
-            for (int j = 0; j < nblk && ok; ++j) {
+                for (int j = 0; j < nblk && ok; ++j) {
 #pragma unroll 1
-                for (int kv = 0; kv < 2; ++kv) {
-                    if (wrap > 0) {
-                        ok = mbar_wait(bar_kv_empty(slot), (wrap - 1) & 1, abort_flag, a.status, kDevLoadWaitEmpty);
-                        if (!ok) break;
-                    }
-                    mbar_arrive_expect_tx(bar_kv_full(slot), kTileBytes);
-                    const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
-#pragma unroll
-                    for (int x = 0; x < kBoxes; ++x)
-                        tma_load_4d(smem_kv(slot) + x * kBoxBytes, tm, bar_kv_full(slot), x * 64, j * T::kBlockN, h, b);
-                    if (++slot == kStages) { slot = 0; ++wrap; }
-                    if (j == 0 && kv == 0 && tile1_valid) {
-                        mbar_arrive_expect_tx(bar_q_full(1), kTileBytes);
+                    for (int kv = 0; kv < 2; ++kv) {
+                        if (wrap > 0) {
+                            ok = mbar_wait(bar_kv_empty(slot), (wrap - 1) & 1, abort_flag, a.status, kDevLoadWaitEmpty);
+                            if (!ok) break;
+                        }
+#ifdef RING_DEBUG_HALF_LOAD
+                        mbar_arrive_expect_tx(bar_kv_full(slot), kBoxBytes);
+                        const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
+                        tma_load_4d(smem_kv(slot), tm, bar_kv_full(slot), 0, j * T::kBlockN, h, b);
+#else
+                        mbar_arrive_expect_tx(bar_kv_full(slot), kTileBytes);
+                        const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
 #pragma unroll
                         for (int x = 0; x < kBoxes; ++x)
-                            tma_load_4d(smem_q(1) + x * kBoxBytes, &tm_q, bar_q_full(1), x * 64, r0 + 128, h, b);
+                            tma_load_4d(smem_kv(slot) + x * kBoxBytes, tm, bar_kv_full(slot), x * 64, j * T::kBlockN, h, b);
+#endif
+                        if (++slot == kStages) { slot = 0; ++wrap; }
+                        if (j == 0 && kv == 0 && tile1_valid) {
+                            mbar_arrive_expect_tx(bar_q_full(1), kTileBytes);
+#pragma unroll
+                            for (int x = 0; x < kBoxes; ++x)
+                                tma_load_4d(smem_q(1) + x * kBoxBytes, &tm_q, bar_q_full(1), x * 64, r0 + 128, h, b);
+                        }
                     }
                 }
             }
-        }
-        __syncwarp();
-    } else if (warp == T::kMmaWarp || warp == T::kMmaWarp + 1) {
-        // ======================================================================= UMMA issuers (one per Q tile)
-        const int t = warp - T::kMmaWarp;
-        if (lane == 0 && nblk > 0 && t < ntiles) {
-            const uint32_t t_s = tmem_base + T::kTmemS0 + t * T::kBlockN;
-            // One half of S_t = Q_t K^T: D/16 instructions of 128 x 64 x 16 against key rows [64 half, 64 half + 64)
-            auto issue_qk_half = [&](int kslot, int half) {
+            __syncwarp();
+        } else if (warp == T::kMmaWarp) {
+            // =================================================================== UMMA issuer: S = Q K^T, both tiles
+            // (One thread sustains roughly one tcgen05.mma per 110 clocks, so the three MMA streams of the CTA
+            //  -- S for both tiles, P V for tile 0, P V for tile 1 -- are issued by three different warps.)
+            if (lane == 0 && nblk > 0) {
+                // S = Q_t K^T into the shared S buffer: D/16 instructions of 128 x 128 x 16
+                auto issue_qk = [&](int t, int kslot) {
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
-                    umma_ss(t_s + half * kHalfN, umma_desc_kmajor_sw128(smem_q(t) + off),
-                            umma_desc_kmajor_sw128(smem_kv(kslot) + half * (kHalfN * 128) + off), kIdescQK,
-                            kk > 0 ? 1u : 0u);
-                }
-            };
-            // O_t (+)= P_t V : kBlockN/16 instructions of 128 x D x 16, A = 16-bit P in TMEM, B = V MN-major
-            auto issue_pv = [&](int vslot, bool accumulate) {
-#pragma unroll
-                for (int kk = 0; kk < T::kBlockN / 16; ++kk) {
-                    umma_ts(tmem_base + T::kTmemO0 + t * D, t_s + T::kTmemPOffset + kk * 8,
-                            umma_desc_mnmajor_sw128(smem_kv(vslot) + kk * 16 * 128, kBoxBytes), kIdescPV,
-                            (accumulate || kk > 0) ? 1u : 0u);
-                }
-            };
-            // K_j is load number 2j of the ring, V_j load number 2j + 1
-            auto ring_slot = [&](int idx) { return idx % kStages; };
-            auto ring_phase = [&](int idx) { return static_cast<uint32_t>((idx / kStages) & 1); };
-
-            // S_t(0), both halves
-            bool ok = mbar_wait(bar_q_full(t), 0, abort_flag, a.status, kDevMmaWaitQ) &&
-                      mbar_wait(bar_kv_full(ring_slot(0)), ring_phase(0), abort_flag, a.status, kDevMmaWaitKV);
-            if (ok) {
-                tcgen05_fence_after_thread_sync();
-                issue_qk_half(ring_slot(0), 0);
-                umma_commit(bar_s_lo_full(t));
-                issue_qk_half(ring_slot(0), 1);
-                umma_commit(bar_s_hi_full(t));
-                umma_commit(bar_kv_empty(ring_slot(0)));
-            }
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = (kk >> 2) * kBoxBytes + (kk & 3) * 32;
+                        umma_ss(tmem_base + T::kTmemS, umma_desc_kmajor_sw128(smem_q(t) + off),
+                                umma_desc_kmajor_sw128(smem_kv(kslot) + off), kIdescQK, kk > 0 ? 1u : 0u);
+                    }
+                };
+                auto ring_slot = [&](int idx) { return idx % kStages; };
+                auto ring_phase = [&](int idx) { return static_cast<uint32_t>((idx / kStages) & 1); };
+                // The S buffer passes S_0(0), S_1(0), S_0(1), S_1(1), ...; read-out number n completes phase n of s_free.
+                int reads = 0;  // read-outs awaited so far
+                bool ok = true;
 #pragma unroll 1
-            for (int j = 0; j < nblk && ok; ++j) {
-                const bool has_next = (j + 1) < nblk;
-                const int kidx = 2 * (j + 1);
-                // lower half of S_t(j + 1): as soon as the warpgroup holds the lower half of S_t(j) in registers
-                if (has_next) {
-                    ok = mbar_wait(bar_s_lo_free(t), j & 1, abort_flag, a.status, kDevMmaWaitS) &&
-                         mbar_wait(bar_kv_full(ring_slot(kidx)), ring_phase(kidx), abort_flag, a.status, kDevMmaWaitKV);
-                    if (!ok) break;
-                    tcgen05_fence_after_thread_sync();
-                    issue_qk_half(ring_slot(kidx), 0);
-                    umma_commit(bar_s_lo_full(t));
-                }
-                // O_t += P_t(j) V_j, then the upper half of S_t(j + 1) over the columns P_t(j) occupied
-                // (the tensor pipe executes one issuer's instructions in order)
-                const int vidx = 2 * j + 1;
-                ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
-                     mbar_wait(bar_kv_full(ring_slot(vidx)), ring_phase(vidx), abort_flag, a.status, kDevMmaWaitKV);
-                if (!ok) break;
-                RING_TRACE_STAMP(true, 6 + t);
-                tcgen05_fence_after_thread_sync();
-                issue_pv(ring_slot(vidx), j > 0);
-                umma_commit(bar_o_done(t));
-                umma_commit(bar_kv_empty(ring_slot(vidx)));
-                if (has_next) {
-                    issue_qk_half(ring_slot(kidx), 1);
-                    umma_commit(bar_s_hi_full(t));
-                    umma_commit(bar_kv_empty(ring_slot(kidx)));
+                for (int j = 0; j < nblk && ok; ++j) {
+                    const int kslot = ring_slot(2 * j);
+#pragma unroll 1
+                    for (int t = 0; t < ntiles; ++t) {
+                        RING_TRACE_STAMP(true, 16 + 4 * t);
+                        if (j == 0) ok = mbar_wait(bar_q_full(t), 0, abort_flag, a.status, kDevMmaWaitQ);
+                        // the buffer is free once its previous content has been read out by the tile it was for
+                        if (ok && (j > 0 || t > 0)) {
+                            ok = mbar_wait(bar_s_free, reads & 1, abort_flag, a.status, kDevMmaWaitS);
+                            ++reads;
+                        }
+                        RING_TRACE_STAMP(true, 17 + 4 * t);
+                        if (ok && t == 0) ok = mbar_wait(bar_kv_full(kslot), ring_phase(2 * j), abort_flag, a.status, kDevMmaWaitKV);
+                        if (!ok) break;
+                        RING_TRACE_STAMP(true, 18 + 4 * t);
+                        tcgen05_fence_after_thread_sync();
+                        issue_qk(t, kslot);
+                        umma_commit(bar_s_full(t));
+                        umma_commit(bar_kv_empty(kslot));  // one arrival per tile
+                        RING_TRACE_STAMP(true, 19 + 4 * t);
+                    }
                 }
             }
+            __syncwarp();
+        } else if (warp == T::kMmaWarp + 1 || warp == T::kMmaWarp + 2) {
+            // =================================================================== UMMA issuer: O_t += P_t V, one warp per tile
+            const int t = warp - (T::kMmaWarp + 1);
+            if (lane == 0 && nblk > 0 && t < ntiles) {
+                // kBlockN/16 instructions of 128 x D x 16, A = 16-bit P in TMEM, B = V MN-major in shared memory
+                auto ring_slot = [&](int idx) { return idx % kStages; };
+                auto ring_phase = [&](int idx) { return static_cast<uint32_t>((idx / kStages) & 1); };
+                bool ok = true;
+#pragma unroll 1
+                for (int j = 0; j < nblk && ok; ++j) {
+                    const int vidx = 2 * j + 1;
+                    const int vslot = ring_slot(vidx);
+                    ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
+                         mbar_wait(bar_kv_full(vslot), ring_phase(vidx), abort_flag, a.status, kDevMmaWaitKV);
+                    if (!ok) break;
+                    RING_TRACE_STAMP(true, 24 + 2 * t);
+                    tcgen05_fence_after_thread_sync();
+#pragma unroll
+                    for (int kk = 0; kk < T::kBlockN / 16; ++kk) {
+                        umma_ts(tmem_base + T::kTmemO0 + t * D, tmem_base + T::kTmemP0 + t * T::kTmemPCols + kk * 8,
+                                umma_desc_mnmajor_sw128(smem_kv(vslot) + kk * 16 * 128, kBoxBytes), kIdescPV,
+                                (j > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    umma_commit(bar_o_done(t));
+                    umma_commit(bar_kv_empty(vslot));  // one arrival per tile
+                    RING_TRACE_STAMP(true, 25 + 2 * t);
+                }
+            }
+            __syncwarp();
         }
-        __syncwarp();
-    } else if (warp < T::kSoftmaxWarps) {
-        // ======================================================================= softmax warpgroups
+    } else {
+        // ############################################################## softmax warpgroups (warps 0..7)
+        setmaxnreg_inc<T::kSoftmaxRegs>();
         const int t = warp >> 2;  // Q tile of this warpgroup
         const int quarter = warp & 3;
         if (t < ntiles) {
             const int row = r0 + t * 128 + quarter * 32 + lane;  // row of the Q shard == TMEM lane
             const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-            const uint32_t t_s = tmem_base + lane_addr + T::kTmemS0 + t * T::kBlockN;
-            const uint32_t t_p = t_s + T::kTmemPOffset;
+            const uint32_t t_s = tmem_base + lane_addr + T::kTmemS;
+            const uint32_t t_p = tmem_base + lane_addr + T::kTmemP0 + t * T::kTmemPCols;
             const uint32_t t_o = tmem_base + lane_addr + T::kTmemO0 + t * D;
             const float c = a.scale_log2;
 
             float m_run = -INFINITY;  // maximum the exponentials are currently taken against (raw score)
             float l_run = 0.f;        // running sum of exp2((s - m_run) c), from unrounded fp32 p
             bool ok = true;
-#if RING_STAGGER_NS > 0
-            if (t == 1) __nanosleep(RING_STAGGER_NS);
-#endif
 
-            auto max64 = [&](const float* s) -> float {
+#pragma unroll 1
+            for (int j = 0; j < nblk; ++j) {
+                uint32_t sr[128];
+                float* s = reinterpret_cast<float*>(sr);
+                ok = mbar_wait(bar_s_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 0);
+                tcgen05_fence_after_thread_sync();
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    tmem_ld_x32(t_s + 32 * i, *reinterpret_cast<uint32_t(*)[32]>(&sr[32 * i]));
+                tmem_wait_ld();
+                // S is in registers: hand the buffer to the other tile (its next S is computed under this softmax)
+                tcgen05_fence_before_thread_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_s_free);
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 1);
+
+                // masking: only blocks that straddle the causal diagonal or the end of the shard
+                const int col0 = j * T::kBlockN;
+                int limit = a.sk - col0;                                  // valid columns of this block
+                if (a.causal) limit = min(limit, row + a.diag - col0 + 1);  // visible columns of this row
+                const bool masked_block = (a.sk - col0 < T::kBlockN) ||
+                                          (a.causal && (r0 + t * 128 + a.diag - col0 + 1) < T::kBlockN);
+                if (masked_block) {
+#pragma unroll
+                    for (int i = 0; i < 128; ++i)
+                        if (i >= limit) s[i] = -INFINITY;
+                }
+
+                // row maximum of the block; adopt it only when it beats the one in use by more than 2^8
 #if RING_USE_MAX3
                 float mx0 = fmax3(s[0], s[1], s[2]), mx1 = fmax3(s[3], s[4], s[5]);
 #pragma unroll
-                for (int i = 6; i + 3 < 64; i += 4) {
+                for (int i = 6; i + 3 < 128; i += 4) {
                     mx0 = fmax3(mx0, s[i], s[i + 1]);
                     mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
                 }
-                return fmax3(mx0, mx1, fmaxf(s[62], s[63]));
+                const float mx = fmax3(mx0, mx1, fmaxf(s[126], s[127]));
 #else
                 float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
 #pragma unroll
-                for (int i = 4; i < 64; i += 4) {
+                for (int i = 4; i < 128; i += 4) {
                     mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]);
                     mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]);
                 }
-                return fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
 #endif
-            };
-            // s[i] <- exp2(s[i] c - ms) in place (fp32, unrounded); returns the sum
-            auto exp64 = [&](float* s, float ms) -> float {
-                const float nms = -ms;
+                float alpha = 1.f;  // factor owed to everything accumulated before this block
+                if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * c > kRescaleThresholdLog2)) {
+                    alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - mx) * c);
+                    m_run = mx;
+                }
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 2);
+
+                // p = exp2(s c - m c), in place, fp32; the sum uses the unrounded values
+                const float nms = (m_run == -INFINITY) ? 0.f : -m_run * c;
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-                for (int i = 0; i < 64; i += 4) {
+                for (int i = 0; i < 128; i += 4) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const float x = fmaf(s[i + u], c, nms);
@@ -335,117 +378,45 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                     }
                     a0 += s[i]; a1 += s[i + 1]; a2 += s[i + 2]; a3 += s[i + 3];
                 }
-                return (a0 + a1) + (a2 + a3);
-            };
-
-            auto pack64 = [&](const float* s, uint32_t (&pk)[32]) {
-#pragma unroll
-                for (int x = 0; x < 32; ++x)
-                    pk[x] = T::kIsBf16 ? pack_bf16x2(s[2 * x], s[2 * x + 1]) : pack_f16x2(s[2 * x], s[2 * x + 1]);
-            };
-
-#pragma unroll 1
-            for (int j = 0; j < nblk; ++j) {
-                uint32_t sr[64];   // one half of the S row, then its probabilities (fp32, in place)
-                uint32_t plo[32];  // lower half of P_t(j) as 16-bit pairs, held until the upper half of S is out of TMEM
-                float* s = reinterpret_cast<float*>(sr);
-                // masking: only blocks that straddle the causal diagonal or the end of the shard
-                const int col0 = j * T::kBlockN;
-                int limit = a.sk - col0;                                  // valid columns of this block
-                if (a.causal) limit = min(limit, row + a.diag - col0 + 1);  // visible columns of this row
-                const bool masked_block = (a.sk - col0 < T::kBlockN) ||
-                                          (a.causal && (r0 + t * 128 + a.diag - col0 + 1) < T::kBlockN);
-                float alpha_tot = 1.f;  // factor owed to everything accumulated before this block
-
-                // ---------------- lower half: key columns [0, 64) of the block
-                ok = mbar_wait(bar_s_lo_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 0);
-                tcgen05_fence_after_thread_sync();
-                tmem_ld_x32(t_s, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-                tmem_ld_x32(t_s + 32, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-                tmem_wait_ld();
-                // those columns are in registers: hand them back so the lower half of S_t(j + 1) is computed meanwhile
-                tcgen05_fence_before_thread_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_s_lo_free(t));
-                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 1);
-                if (masked_block) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (i >= limit) s[i] = -INFINITY;
-                }
-                {
-                    const float mx = max64(s);
-                    if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * c > kRescaleThresholdLog2)) {
-                        alpha_tot = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - mx) * c);
-                        m_run = mx;
-                    }
-                }
-                float ms = (m_run == -INFINITY) ? 0.f : m_run * c;
-                float l_blk = exp64(s, ms);
-                pack64(s, plo);
-                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 2);
-
-                // ---------------- upper half: key columns [64, 128); it is written after P_t(j - 1) was consumed
-                ok = mbar_wait(bar_s_hi_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
-                ok = __all_sync(0xffffffffu, ok);
-                if (!ok) break;
-                tcgen05_fence_after_thread_sync();
-                tmem_ld_x32(t_s + 64, *reinterpret_cast<uint32_t(*)[32]>(&sr[0]));
-                tmem_ld_x32(t_s + 96, *reinterpret_cast<uint32_t(*)[32]>(&sr[32]));
-                tmem_wait_ld();
+                l_run = fmaf(l_run, alpha, (a0 + a1) + (a2 + a3));
                 RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 3);
-                if (masked_block) {
+
+                // P_t(j - 1) V must be complete before P_t is overwritten or O_t rescaled (it long is)
+                if (j > 0) {
+                    ok = mbar_wait(bar_o_done(t), (j - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tcgen05_fence_after_thread_sync();
+                    // O_t is rescaled only when some row of the warp adopted a new maximum (warp-collective TMEM round trip)
+                    if (__any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (64 + i >= limit) s[i] = -INFINITY;
-                }
-                {
-                    const float mx = max64(s);
-                    if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * c > kRescaleThresholdLog2)) {
-                        // the lower half was taken against the old maximum: bring it to the new one
-                        const float al = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - mx) * c);
+                        for (int i = 0; i < D / 32; ++i) {
+                            uint32_t orr[32];
+                            tmem_ld_x32(t_o + 32 * i, orr);
+                            tmem_wait_ld();
 #pragma unroll
-                        for (int x = 0; x < 32; ++x) plo[x] = T::kIsBf16 ? scale_bf16x2(plo[x], al) : scale_f16x2(plo[x], al);
-                        l_blk *= al;
-                        alpha_tot *= al;
-                        m_run = mx;
-                        ms = m_run * c;
+                            for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha);
+                            tmem_st_x32(t_o + 32 * i, orr);
+                        }
                     }
                 }
-                l_blk += exp64(s, ms);
-                l_run = fmaf(l_run, alpha_tot, l_blk);
-                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 5);
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 4);
 
-                // O_t is rescaled only when some row of the warp adopted a new maximum (a warp-collective TMEM
-                // round trip).  S_hi(j) complete implies P_t(j - 1) V is complete: nothing of this tile is in flight.
-                if (j > 0 && __any_sync(0xffffffffu, alpha_tot != 1.f)) {
+                // P_t(j): 128 probabilities -> 64 columns of 16-bit pairs
 #pragma unroll
-                    for (int i = 0; i < D / 32; ++i) {
-                        uint32_t orr[32];
-                        tmem_ld_x32(t_o + 32 * i, orr);
-                        tmem_wait_ld();
+                for (int i = 0; i < 2; ++i) {
+                    uint32_t pk[32];
 #pragma unroll
-                        for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha_tot);
-                        tmem_st_x32(t_o + 32 * i, orr);
-                    }
+                    for (int x = 0; x < 32; ++x)
+                        pk[x] = T::kIsBf16 ? pack_bf16x2(s[64 * i + 2 * x], s[64 * i + 2 * x + 1])
+                                           : pack_f16x2(s[64 * i + 2 * x], s[64 * i + 2 * x + 1]);
+                    tmem_st_x32(t_p + 32 * i, pk);
                 }
-
-                // P_t(j): 128 probabilities -> 64 packed columns over the upper half of S_t
-                tmem_st_x32(t_p, plo);
-                {
-                    uint32_t phi[32];
-                    pack64(s, phi);
-                    tmem_st_x32(t_p + 32, phi);
-                }
-                RING_TRACE_STAMP(quarter == 0 && lane == 0, 14 + t);
                 tmem_wait_st();
                 tcgen05_fence_before_thread_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar_p_full(t));  // one arrival per warp (barrier count 4)
-                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 4);
+                if (lane == 0) mbar_arrive(bar_p_full(t));
+                RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 5);
             }
 
             // ---- epilogue: O / l, LSE, optional fold into an earlier partial -----------------------

@@ -51,9 +51,13 @@ struct Ring_fwd_traits : public Base
     // ---- warp roles -----------------------------------------------------------------------
     static constexpr int kQTiles = kBlockM / Base::kUmmaM;       // 2: ping-pong pair
     static constexpr int kSoftmaxWarps = 4 * kQTiles;            // one warpgroup per Q tile, 1 thread = 1 row
-    static constexpr int kMmaWarp = kSoftmaxWarps;               // warps 8, 9: single-thread UMMA issue for Q tile 0, 1
-    static constexpr int kLoadWarp = kSoftmaxWarps + kQTiles;    // warp 10: single-thread TMA issue (warp 11 idles)
-    static_assert(kNWarps == kSoftmaxWarps + 4, "8 softmax warps + one producer warpgroup (2 MMA, 1 load, 1 spare)");
+    static constexpr int kMmaWarp = kSoftmaxWarps;               // warp 8: issues S = Q K^T; warps 9, 10: P V of tile 0, 1
+    static constexpr int kLoadWarp = kSoftmaxWarps + 3;          // warp 11: single-thread TMA issue
+    static_assert(kNWarps == kSoftmaxWarps + 4, "8 softmax warps + one producer warpgroup (3 UMMA issuers, 1 loader)");
+    // Registers after setmaxnreg: 256 softmax threads x kSoftmaxRegs + 128 producer threads x kProducerRegs <= 64 Ki
+    static constexpr int kSoftmaxRegs = 216;
+    static constexpr int kProducerRegs = 72;
+    static_assert(256 * kSoftmaxRegs + 128 * kProducerRegs <= 65536, "register file");
 
 
     // ---- shared memory ----------------------------------------------------------------------
@@ -61,15 +65,16 @@ struct Ring_fwd_traits : public Base
     static constexpr int kBoxBytes = 128 * Base::kSwizzleElems * 2;            // 16 KiB
     static constexpr int kTileBytes = kBoxesPerTile * kBoxBytes;               // one 128 x kHeadDim tile
     static constexpr int kStages = kHeadDim == 128 ? 5 : 8;                    // K/V ring slots (K and V alternate)
-    static constexpr int kNumBarriers = 2 /*q_full*/ + 2 * kStages + 5 * kQTiles /*s_lo_full,s_hi_full,s_lo_free,p_full,o_done*/;
+    static constexpr int kNumBarriers = 2 /*q_full*/ + 2 * kStages + 3 * kQTiles /*s_full,p_full,o_done*/ + 1 /*s_free*/;
     static constexpr int kSmemTiles = (kQTiles + kStages) * kTileBytes;
     static constexpr int kSmemSize = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers, TMEM slot, flags*/;
     static_assert(kSmemSize <= 227 * 1024, "exceeds the 227 KiB per-CTA limit");
 
     // ---- tensor memory (512 columns x 128 lanes x 32 bit) ------------------------------------------
     static constexpr int kTmemCols = 512;
-    static constexpr int kTmemS0 = 0;                 // S tile t at columns t*128; 16-bit P aliases its UPPER 64 columns
-    static constexpr int kTmemPOffset = kBlockN / 2;  // so that the lower half of the next S can be written early
-    static constexpr int kTmemO0 = kQTiles * kBlockN; // O tile t at kTmemO0 + t*kHeadDim
+    static constexpr int kTmemS = 0;                  // ONE S buffer (128 fp32 columns) used by the two Q tiles in turn
+    static constexpr int kTmemPCols = kBlockN / 2;    // 16-bit P of a tile: 64 columns of its own
+    static constexpr int kTmemP0 = kBlockN;           // P tile t at kTmemP0 + t*kTmemPCols
+    static constexpr int kTmemO0 = kBlockN + kQTiles * kTmemPCols;  // O tile t at kTmemO0 + t*kHeadDim
     static_assert(kTmemO0 + kQTiles * kHeadDim <= kTmemCols, "TMEM budget");
 };
