@@ -82,6 +82,9 @@ constexpr float kRescaleThresholdLog2 = 8.0f;
 #ifndef RING_USE_MAX3
 #define RING_USE_MAX3 1  // three-input max.f32 in the row-maximum reduction
 #endif
+#ifndef RING_PV_AFTER_QK
+#define RING_PV_AFTER_QK 0
+#endif
 #ifndef RING_POLY_EVERY
 #define RING_POLY_EVERY 0  // N > 0: every N-th exponential is evaluated on the FMA pipe instead of the MUFU
 #endif
@@ -182,15 +185,18 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 #pragma unroll
                 for (int x = 0; x < kBoxes; ++x)
                     tma_load_4d(smem_q(0) + x * kBoxBytes, &tm_q, bar_q_full(0), x * 64, r0, h, b);
-                int slot = 0;
-                uint32_t wrap = 0;  // how many times the ring has wrapped
+                // K and V have rings of their own (kKStages and kVStages slots): a K slot is free as soon as both
+                // tiles' S products have read it, which is early, so K_(j+1) never queues behind a late P V.
                 bool ok = true;
 #pragma unroll 1
                 for (int j = 0; j < nblk && ok; ++j) {
 #pragma unroll 1
                     for (int kv = 0; kv < 2; ++kv) {
-                        if (wrap > 0) {
-                            ok = mbar_wait(bar_kv_empty(slot), (wrap - 1) & 1, abort_flag, a.status, kDevLoadWaitEmpty);
+                        const int nslots = kv == 0 ? T::kKStages : T::kVStages;
+                        const int slot = (kv == 0 ? 0 : T::kKStages) + j % nslots;
+                        const int use = j / nslots;  // how many times this slot has been filled before
+                        if (use > 0) {
+                            ok = mbar_wait(bar_kv_empty(slot), (use - 1) & 1, abort_flag, a.status, kDevLoadWaitEmpty);
                             if (!ok) break;
                         }
 #ifdef RING_DEBUG_HALF_LOAD
@@ -204,7 +210,6 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         for (int x = 0; x < kBoxes; ++x)
                             tma_load_4d(smem_kv(slot) + x * kBoxBytes, tm, bar_kv_full(slot), x * 64, j * T::kBlockN, h, b);
 #endif
-                        if (++slot == kStages) { slot = 0; ++wrap; }
                         if (j == 0 && kv == 0 && tile1_valid) {
                             mbar_arrive_expect_tx(bar_q_full(1), kTileBytes);
 #pragma unroll
@@ -229,14 +234,13 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                                 umma_desc_kmajor_sw128(smem_kv(kslot) + off), kIdescQK, kk > 0 ? 1u : 0u);
                     }
                 };
-                auto ring_slot = [&](int idx) { return idx % kStages; };
-                auto ring_phase = [&](int idx) { return static_cast<uint32_t>((idx / kStages) & 1); };
                 // The S buffer passes S_0(0), S_1(0), S_0(1), S_1(1), ...; read-out number n completes phase n of s_free.
                 int reads = 0;  // read-outs awaited so far
                 bool ok = true;
 #pragma unroll 1
                 for (int j = 0; j < nblk && ok; ++j) {
-                    const int kslot = ring_slot(2 * j);
+                    const int kslot = j % T::kKStages;
+                    const uint32_t kphase = static_cast<uint32_t>((j / T::kKStages) & 1);
 #pragma unroll 1
                     for (int t = 0; t < ntiles; ++t) {
                         RING_TRACE_STAMP(true, 16 + 4 * t);
@@ -247,7 +251,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                             ++reads;
                         }
                         RING_TRACE_STAMP(true, 17 + 4 * t);
-                        if (ok && t == 0) ok = mbar_wait(bar_kv_full(kslot), ring_phase(2 * j), abort_flag, a.status, kDevMmaWaitKV);
+                        if (ok && t == 0) ok = mbar_wait(bar_kv_full(kslot), kphase, abort_flag, a.status, kDevMmaWaitKV);
                         if (!ok) break;
                         RING_TRACE_STAMP(true, 18 + 4 * t);
                         tcgen05_fence_after_thread_sync();
@@ -264,16 +268,26 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             const int t = warp - (T::kMmaWarp + 1);
             if (lane == 0 && nblk > 0 && t < ntiles) {
                 // kBlockN/16 instructions of 128 x D x 16, A = 16-bit P in TMEM, B = V MN-major in shared memory
-                auto ring_slot = [&](int idx) { return idx % kStages; };
-                auto ring_phase = [&](int idx) { return static_cast<uint32_t>((idx / kStages) & 1); };
                 bool ok = true;
 #pragma unroll 1
                 for (int j = 0; j < nblk && ok; ++j) {
-                    const int vidx = 2 * j + 1;
-                    const int vslot = ring_slot(vidx);
+                    const int vslot = T::kKStages + j % T::kVStages;
+                    const uint32_t vphase = static_cast<uint32_t>((j / T::kVStages) & 1);
                     ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
-                         mbar_wait(bar_kv_full(vslot), ring_phase(vidx), abort_flag, a.status, kDevMmaWaitKV);
+                         mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV);
                     if (!ok) break;
+#if RING_PV_AFTER_QK
+                    // Tile t has just finished block j and is reading its S(j + 1): that read-out releases the S
+                    // buffer for the OTHER tile's next S, which the other tile will soon be waiting for, while this
+                    // PV product has a whole softmax of slack.  Let that S go through the tensor pipe first.
+                    if (ntiles == 2) {
+                        const int jn = t == 0 ? j + 1 : j + 2;  // block whose S the other tile gets now
+                        if (jn < nblk) {
+                            ok = mbar_wait(bar_s_full(t ^ 1), jn & 1, abort_flag, a.status, kDevMmaWaitS);
+                            if (!ok) break;
+                        }
+                    }
+#endif
                     RING_TRACE_STAMP(true, 24 + 2 * t);
                     tcgen05_fence_after_thread_sync();
 #pragma unroll

@@ -64,7 +64,9 @@ struct Ring_fwd_traits : public Base
     static constexpr int kBoxesPerTile = kHeadDim / Base::kSwizzleElems;       // TMA boxes per 128-row tile
     static constexpr int kBoxBytes = 128 * Base::kSwizzleElems * 2;            // 16 KiB
     static constexpr int kTileBytes = kBoxesPerTile * kBoxBytes;               // one 128 x kHeadDim tile
-    static constexpr int kStages = kHeadDim == 128 ? 5 : 8;                    // K/V ring slots (K and V alternate)
+    static constexpr int kStages = kHeadDim == 128 ? 5 : 8;                    // K/V slots in shared memory
+    static constexpr int kKStages = kHeadDim == 128 ? 2 : 3;                   // ... of which the K ring
+    static constexpr int kVStages = kStages - kKStages;                        // ... and the V ring
     static constexpr int kNumBarriers = 2 /*q_full*/ + 2 * kStages + 3 * kQTiles /*s_full,p_full,o_done*/ + 1 /*s_free*/;
     static constexpr int kSmemTiles = (kQTiles + kStages) * kTileBytes;
     static constexpr int kSmemSize = kSmemTiles + 1024 /*alignment slack*/ + 256 /*barriers, TMEM slot, flags*/;
