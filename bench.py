@@ -207,9 +207,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         ctx.forward(q, k, v, out, lse, softmax_scale=scale)
 
     def step_e2e():
-        q.copy_(hq, non_blocking=True); k.copy_(hk, non_blocking=True); v.copy_(hv, non_blocking=True)
-        ctx.forward(q, k, v, out, lse, softmax_scale=scale)
-        h_out.copy_(out, non_blocking=True); h_lse.copy_(lse, non_blocking=True)
+        # the public host-buffer call: pinned Q, K, V in, pinned O, LSE out, copies inside the timed region
+        ctx.forward_host(hq, hk, hv, h_out, h_lse, chunks=args.e2e_chunks, softmax_scale=scale)
 
     def timed(fn, steps):
         barrier()
@@ -339,6 +338,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-chunks", type=int, default=8, help="(batch, head) groups the host-buffer forward pipelines")
     ap.add_argument("--prewarm-ms", type=float, default=400.0, help="untimed work before the timed region (power-steady clocks)")
     ap.add_argument("--transport", default="default", choices=["default", "nccl", "peer"], help="K/V exchange transport")
     ap.add_argument("--merge-mode", type=int, default=None, choices=[0, 1], help="0 separate merge kernel, 1 fused epilogue")

@@ -112,6 +112,16 @@ int ring_ctx_set_local_shards(RingCtx* ctx, const void* const* k_shards, const v
 int ring_attention_fwd(RingCtx* ctx, const struct Ring_fwd_params* params);
 
 /*
+ * Same forward for callers whose tensors live in (pinned) HOST memory, as the reference's driver fills them
+ * (initQKV, csrc/ring_attention.cu:731-748, builds on the host and copies).  q/k/v/out/lse of `params` are host
+ * pointers; the (batch, head) slabs are processed in `chunks` groups so that the copy in of one group, the ring
+ * forward of the previous and the copy out of the one before overlap.  Collective like ring_attention_fwd
+ * (every rank: same shapes, same chunks).  Asynchronous on params->stream: when that stream reaches the end of the
+ * call, the results are in the host buffers.
+ */
+int ring_attention_fwd_host(RingCtx* ctx, const struct Ring_fwd_params* params, int chunks);
+
+/*
  * The schedule run_ring_fwd follows, as pure host logic (no GPU needed): step `step` of rank `rank`.
  * Restates the loop header of ring_attention_kernel (csrc/ring_attention.cu:456-470, 611-619): the shard
  * visited at step i is that of PE (mype + i) % npes, fetched from its origin PE.

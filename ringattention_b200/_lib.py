@@ -61,6 +61,7 @@ SYMBOLS = {
     "ring_ctx_create_local": (c_int, [ctypes.POINTER(c_void_p), c_int]),
     "ring_ctx_set_local_shards": (c_int, [c_void_p, ctypes.POINTER(c_void_p), ctypes.POINTER(c_void_p)]),
     "ring_attention_fwd": (c_int, [c_void_p, ctypes.POINTER(Ring_fwd_params)]),
+    "ring_attention_fwd_host": (c_int, [c_void_p, ctypes.POINTER(Ring_fwd_params), c_int]),
     "ring_ctx_synchronize": (c_int, [c_void_p]),
     "ring_step_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(RingStepPlan)]),
     "ring_ctx_get_timings": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_float), ctypes.POINTER(c_float), c_int]),

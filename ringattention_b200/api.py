@@ -183,6 +183,29 @@ class RingContext:
                              causal=causal, softmax_scale=softmax_scale, stream=stream)
         self.forward_params(p)
 
+    def forward_host(self, q, k, v, out, lse=None, *, chunks: int = 4, causal: bool = False,
+                     softmax_scale: Optional[float] = None, stream=None, rank: Optional[int] = None) -> None:
+        """Same forward with HOST tensors (pinned CPU torch tensors [B, H, S_local, D]): copies in, computes and
+        copies out in `chunks` overlapping groups of (batch, head) slabs.  Asynchronous on `stream`; when the
+        stream reaches the end of the call, `out` / `lse` hold the results."""
+        import torch
+        B, H, S, D = q.shape
+        for x, n in ((q, "q"), (k, "k"), (v, "v"), (out, "out")):
+            if x.is_cuda or not x.is_contiguous() or not x.is_pinned():
+                raise ValueError(f"{n} must be a contiguous pinned host tensor")
+            if tuple(x.shape) != (B, H, S, D):
+                raise ValueError("q, k, v, out must all be [B, H, S_local, D]")
+        if q.dtype not in _half_types() or out.dtype != torch.float32:
+            raise ValueError("q, k, v must be fp16/bf16 and out fp32")
+        if lse is not None and (lse.is_cuda or not lse.is_pinned() or tuple(lse.shape) != (B, H, S)):
+            raise ValueError("lse must be a pinned host tensor [B, H, S_local]")
+        mype = self.rank if rank is None else int(rank)
+        p = set_params_fprop(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), self.world, mype, [S] * self.world,
+                             D, S, batch=B, heads=H, lse=None if lse is None else lse.data_ptr(), causal=causal,
+                             softmax_scale=softmax_scale, stream=stream)
+        p.is_bf16 = int(q.dtype == torch.bfloat16)
+        check(_lib.load().ring_attention_fwd_host(self._h, ctypes.byref(p), int(chunks)), "ring_attention_fwd_host")
+
     def synchronize(self) -> None:
         check(_lib.load().ring_ctx_synchronize(self._h), "ring_ctx_synchronize")
 

@@ -387,6 +387,13 @@ struct RingCtx {
     cudaEvent_t ev_push_done = nullptr;
     cudaEvent_t ev_call_done = nullptr;  // end of the previous call on whatever stream it used
     bool have_call_done = false;
+    // ---- host-buffer forward (ring_attention_fwd_host): two staging sets, copy streams, per-chunk events
+    void* stage_in[2] = {nullptr, nullptr};   // [q | k | v] of one chunk
+    void* stage_out[2] = {nullptr, nullptr};  // [out | lse] of one chunk
+    size_t stage_in_cap[2] = {0, 0}, stage_out_cap[2] = {0, 0};
+    cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
+    cudaEvent_t ev_h2d[kMaxWorld] = {}, ev_comp[kMaxWorld] = {}, ev_d2h[kMaxWorld] = {};
+    bool host_ready = false;
 };
 
 constexpr int kFlagReady = 0;
@@ -957,6 +964,15 @@ int ring_ctx_destroy(RingCtx* c) {
     if (c->recv_block) { cudaFree(c->recv_block); c->recv[0] = c->recv[1] = nullptr; }
     if (c->flags) cudaFree(c->flags);
     if (c->xchg_dev) cudaFree(c->xchg_dev);
+    for (int i = 0; i < 2; ++i) {
+        if (c->stage_in[i]) cudaFree(c->stage_in[i]);
+        if (c->stage_out[i]) cudaFree(c->stage_out[i]);
+    }
+    if (c->host_ready) {
+        for (int i = 0; i < kMaxWorld; ++i) { cudaEventDestroy(c->ev_h2d[i]); cudaEventDestroy(c->ev_comp[i]); cudaEventDestroy(c->ev_d2h[i]); }
+        cudaStreamDestroy(c->h2d_stream);
+        cudaStreamDestroy(c->d2h_stream);
+    }
     if (c->ev_push_done) cudaEventDestroy(c->ev_push_done);
     if (c->ev_call_done) cudaEventDestroy(c->ev_call_done);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
@@ -979,6 +995,72 @@ int ring_attention_fwd(RingCtx* ctx, const struct Ring_fwd_params* params) {
     int rc = validate_params(ctx, params);
     if (rc) return rc;
     return run_ring_fwd(ctx, *params, params->stream);
+}
+
+// Host-buffer forward: the (batch, head) slabs are independent, so they are taken `chunks` groups at a time and the
+// host-to-device copy of group c + 1, the ring forward of group c and the device-to-host copy of group c - 1 overlap
+// (PCIe is full duplex).  Every rank of the context must call it with the same shapes and chunk count.
+int ring_attention_fwd_host(RingCtx* c, const struct Ring_fwd_params* hp, int chunks) {
+    int rc = validate_params(c, hp);
+    if (rc) return rc;
+    const int B = hp->batch > 0 ? hp->batch : 1, H = hp->heads > 0 ? hp->heads : 1;
+    const int slabs = B * H;
+    if (chunks < 1) chunks = 1;
+    if (chunks > slabs) chunks = slabs;
+    if (chunks > kMaxWorld) chunks = kMaxWorld;
+    const int S = hp->h_seqlen[hp->mype], D = hp->dim;
+    const size_t slab_in = static_cast<size_t>(S) * D * 2, slab_out = static_cast<size_t>(S) * D * 4, slab_lse = static_cast<size_t>(S) * 4;
+    const int per = (slabs + chunks - 1) / chunks;
+    if (!c->host_ready) {
+        RING_CUDA(cudaStreamCreateWithFlags(&c->h2d_stream, cudaStreamNonBlocking));
+        RING_CUDA(cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
+        for (int i = 0; i < kMaxWorld; ++i) {
+            RING_CUDA(cudaEventCreateWithFlags(&c->ev_h2d[i], cudaEventDisableTiming));
+            RING_CUDA(cudaEventCreateWithFlags(&c->ev_comp[i], cudaEventDisableTiming));
+            RING_CUDA(cudaEventCreateWithFlags(&c->ev_d2h[i], cudaEventDisableTiming));
+        }
+        c->host_ready = true;
+    }
+    for (int i = 0; i < 2; ++i) {
+        if ((rc = grow(&c->stage_in[i], &c->stage_in_cap[i], 3 * per * slab_in))) return rc;
+        if ((rc = grow(&c->stage_out[i], &c->stage_out_cap[i], per * (slab_out + slab_lse)))) return rc;
+    }
+    cudaStream_t cs = hp->stream;
+    // the copies may start once the caller's stream has reached this point (the host buffers are then ready)
+    RING_CUDA(cudaEventRecord(c->ev_fork, cs));
+    RING_CUDA(cudaStreamWaitEvent(c->h2d_stream, c->ev_fork, 0));
+    RING_CUDA(cudaStreamWaitEvent(c->d2h_stream, c->ev_fork, 0));
+    int nch = 0;
+    for (int s0 = 0; s0 < slabs; s0 += per, ++nch) {
+        const int n = (slabs - s0) < per ? (slabs - s0) : per;
+        const int set = nch & 1;
+        char* dq = static_cast<char*>(c->stage_in[set]);
+        char* dk = dq + per * slab_in;
+        char* dv = dk + per * slab_in;
+        char* dout = static_cast<char*>(c->stage_out[set]);
+        char* dlse = dout + per * slab_out;
+        if (nch >= 2) RING_CUDA(cudaStreamWaitEvent(c->h2d_stream, c->ev_comp[nch - 2], 0));  // staging set reuse
+        RING_CUDA(cudaMemcpyAsync(dq, static_cast<const char*>(hp->q_ptr) + s0 * slab_in, n * slab_in, cudaMemcpyHostToDevice, c->h2d_stream));
+        RING_CUDA(cudaMemcpyAsync(dk, static_cast<const char*>(hp->k_ptr) + s0 * slab_in, n * slab_in, cudaMemcpyHostToDevice, c->h2d_stream));
+        RING_CUDA(cudaMemcpyAsync(dv, static_cast<const char*>(hp->v_ptr) + s0 * slab_in, n * slab_in, cudaMemcpyHostToDevice, c->h2d_stream));
+        RING_CUDA(cudaEventRecord(c->ev_h2d[nch], c->h2d_stream));
+        RING_CUDA(cudaStreamWaitEvent(cs, c->ev_h2d[nch], 0));
+        if (nch >= 2) RING_CUDA(cudaStreamWaitEvent(cs, c->ev_d2h[nch - 2], 0));
+        Ring_fwd_params p = *hp;
+        p.batch = 1;
+        p.heads = n;
+        p.q_ptr = dq; p.k_ptr = dk; p.v_ptr = dv; p.out_ptr = dout; p.lse_ptr = dlse;
+        if ((rc = run_ring_fwd(c, p, cs))) return rc;
+        RING_CUDA(cudaEventRecord(c->ev_comp[nch], cs));
+        RING_CUDA(cudaStreamWaitEvent(c->d2h_stream, c->ev_comp[nch], 0));
+        RING_CUDA(cudaMemcpyAsync(static_cast<char*>(hp->out_ptr) + s0 * slab_out, dout, n * slab_out, cudaMemcpyDeviceToHost, c->d2h_stream));
+        if (hp->lse_ptr)
+            RING_CUDA(cudaMemcpyAsync(static_cast<char*>(hp->lse_ptr) + s0 * slab_lse, dlse, n * slab_lse, cudaMemcpyDeviceToHost, c->d2h_stream));
+        RING_CUDA(cudaEventRecord(c->ev_d2h[nch], c->d2h_stream));
+    }
+    // complete on the caller's stream only when the last results are on the host
+    for (int i = nch > 2 ? nch - 2 : 0; i < nch; ++i) RING_CUDA(cudaStreamWaitEvent(cs, c->ev_d2h[i], 0));
+    return RING_OK;
 }
 
 int ring_ctx_synchronize(RingCtx* ctx) {
