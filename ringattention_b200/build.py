@@ -13,6 +13,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libringattn_b200.so")
 SOURCES = [os.path.join(CSRC, "ring_attention.cu")]
+MAIN = os.path.join(HERE, "ring_attention_main")            # the reference's driver executable, over the library
+MAIN_SOURCE = os.path.join(CSRC, "ring_attention_main.cu")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-shared", "-Xcompiler", "-fPIC",
@@ -27,7 +29,7 @@ def _nvcc() -> str:
 
 
 def _stale() -> bool:
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(MAIN):
         return True
     t = os.path.getmtime(LIB)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)]
@@ -47,6 +49,12 @@ def build(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
         if verbose:
             print(res.stderr)
+        # driver executable mirroring the reference's main(); finds the library next to itself
+        cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-o", MAIN, MAIN_SOURCE,
+               "-L" + HERE, "-lringattn_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("nvcc failed on the driver executable:\n" + res.stdout + res.stderr)
     return LIB
 
 

@@ -282,8 +282,11 @@ int validate_block(const BlockLaunch& L) {
     if (L.dim != 64 && L.dim != 128) return fail(RING_ERR_INVALID_ARGUMENT, "dim must be 64 or 128, got %d", L.dim);
     if (L.batch <= 0 || L.heads <= 0 || L.sq <= 0 || L.sk <= 0)
         return fail(RING_ERR_INVALID_ARGUMENT, "batch, heads and sequence lengths must be positive");
-    if (L.sq % 128 != 0 || L.sk % 128 != 0)
-        return fail(RING_ERR_INVALID_ARGUMENT, "sequence lengths must be multiples of 128 (got %d, %d)", L.sq, L.sk);
+    // Any length is accepted: rows past the end of a shard are read as zero by the tensor maps, masked in the
+    // softmax (keys) or simply not stored (queries).  The reference needs multiples of its 64-row tile
+    // (no predication, csrc/ring_attention.cu:131,143-145).
+    if (L.sq > (1 << 24) || L.sk > (1 << 24))
+        return fail(RING_ERR_INVALID_ARGUMENT, "sequence lengths above 2^24 rows per shard are not supported");
     if (static_cast<int64_t>(L.batch) * L.heads > 65535)
         return fail(RING_ERR_INVALID_ARGUMENT, "batch * heads must not exceed 65535");
     if (!(L.scale > 0.f) || !std::isfinite(L.scale))
@@ -786,8 +789,8 @@ int validate_params(RingCtx* c, const Ring_fwd_params* p) {
         if (p->h_seqlen[i] != p->h_seqlen[0])
             return fail(RING_ERR_INVALID_ARGUMENT, "uneven shards are not supported (seqlen[%d] = %d, seqlen[0] = %d)", i,
                         p->h_seqlen[i], p->h_seqlen[0]);
-    if (p->h_seqlen[0] <= 0 || p->h_seqlen[0] % 128 != 0)
-        return fail(RING_ERR_INVALID_ARGUMENT, "seqlen per rank must be a positive multiple of 128, got %d", p->h_seqlen[0]);
+    if (p->h_seqlen[0] <= 0)
+        return fail(RING_ERR_INVALID_ARGUMENT, "seqlen per rank must be positive, got %d", p->h_seqlen[0]);
     if (!(p->softmax_scale > 0.f) || !std::isfinite(p->softmax_scale))
         return fail(RING_ERR_INVALID_ARGUMENT, "softmax_scale must be positive and finite");
     int dev = -1;

@@ -45,7 +45,7 @@ def test_params_struct_matches_reference_prefix():
 
 @pytest.mark.parametrize("kwargs,needle", [
     (dict(dim=96), "dim must be 64 or 128"),
-    (dict(sq=100), "multiples of 128"),
+    (dict(sq=(1 << 24) + 1), "2^24"),
     (dict(sk=0), "must be positive"),
     (dict(q=0), "null tensor pointer"),
     (dict(scale=0.0), "softmax_scale"),

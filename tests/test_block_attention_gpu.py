@@ -85,6 +85,23 @@ def test_block_noncausal(ra, shape):
     assert_parity(o, lse, want_o, want_lse, f"block {shape}")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("shape", [(1, 2, 200, 333, 128), (2, 1, 1, 1, 64), (1, 1, 129, 127, 64), (1, 3, 300, 1000, 128),
+                                   (1, 1, 257, 64, 128)], ids=lambda s: "x".join(map(str, s)))
+def test_block_ragged_lengths(ra, shape, causal):
+    """Lengths that are not multiples of the 128-row tile (the reference has no tail predication at all):
+    out-of-range key rows are masked, out-of-range query rows are not stored."""
+    B, H, Sq, Sk, D = shape
+    q = synthetic.make_shard("q", 900 + Sq, B, H, D, 0, Sq)
+    k = synthetic.make_shard("k", 900 + Sq, B, H, D, 0, Sk)
+    v = synthetic.make_shard("v", 900 + Sq, B, H, D, 0, Sk)
+    scale = D ** -0.5
+    q_off = max(Sk - Sq, 0) if causal else 0   # align the ends so that every row sees at least one key
+    o, lse = _run_block(ra, q, k, v, scale, causal, q_off, 0)
+    want_o, want_lse = oracle.attention_fwd(q, k, v, scale, causal, q_off, 0)
+    assert_parity(o, lse, want_o, want_lse, f"ragged {shape} causal={causal}")
+
+
 @pytest.mark.parametrize("offs", [(0, 0), (256, 0), (0, 256), (128, 384), (1024, 0), (0, 1024)],
                          ids=lambda o: f"q{o[0]}k{o[1]}")
 @pytest.mark.parametrize("D", [64, 128])

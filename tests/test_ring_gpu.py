@@ -64,6 +64,17 @@ def test_virtual_ring_d64_three_ranks(ra):
     assert_parity(o, lse, want_o, want_lse, "ring d64 world=3")
 
 
+def test_virtual_ring_ragged_shard_length(ra):
+    """Shards of 200 rows (not a multiple of the tile): causal ring over 3 virtual ranks."""
+    B, H, D, world = 1, 2, 128, 3
+    S = 200 * world
+    q, k, v = synthetic.make_qkv(5151, B, H, D, 0, S)
+    for causal in (False, True):
+        o, lse = _ring_local(ra, q, k, v, world, D ** -0.5, causal, 1)
+        want_o, want_lse = oracle.attention_fwd(q, k, v, D ** -0.5, causal)
+        assert_parity(o, lse, want_o, want_lse, f"ragged ring causal={causal}")
+
+
 def test_context_rejects_mismatched_calls(ra):
     import torch
     ctx = ra.RingContext.create_local(2)
@@ -98,3 +109,22 @@ def test_host_buffer_forward_matches_oracle(ra, chunks):
         want_o, want_lse = oracle.attention_fwd(q, k, v, D ** -0.5, True)
         assert_parity(ho.numpy(), hl.numpy(), want_o, want_lse, f"host forward chunks={chunks}")
     ctx.destroy()
+
+
+def test_reference_driver_executable(ra):
+    """The C++ driver that mirrors the reference's main() (csrc/ring_attention.cu:750-790): its 8x8 corner must be
+    the attention of the deterministic fill (:731-741), and it reports a time per call."""
+    import os
+    import re
+    import subprocess
+    exe = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "ringattention_b200", "ring_attention_main")
+    env = dict(os.environ, RING_SEQ="1024", RING_WARMUP="2", RING_LOOPS="3")
+    res = subprocess.run([exe], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
+    lines = res.stdout.strip().splitlines()
+    assert lines[0] == "mype: 0 success" and lines[-1].startswith("elapsedtime=")
+    corner = np.array([[float(x) for x in ln.split()] for ln in lines[1:9]], dtype=np.float32)
+    f = oracle.fill_with_num(1024, 64)[None, None]
+    want, _ = oracle.attention_fwd(f, f, f, 64 ** -0.5)
+    assert np.abs(corner - want[0, 0, :8, :8]).max() <= 2e-3 * max(1.0, float(np.abs(want).max()))
+    assert float(re.sub("elapsedtime=", "", lines[-1])) > 0
