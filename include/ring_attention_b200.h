@@ -13,7 +13,8 @@
  *     O [batch, heads, seqlen_local, dim] fp32, LSE [batch, heads, seqlen_local] fp32 (natural log);
  *     per (batch, head) this is the reference's [seqlen, dim] row-major matrix
  *     (csrc/ring_attention.cu:422-454); all base pointers 16-byte aligned;
- *   - dim is 64 or 128; seqlen_local is a multiple of 128 and equal on all ranks;
+ *   - dim is 64 or 128; every rank holds at least one row; shard lengths need neither be equal (seqlen[] per PE as
+ *     in csrc/ring.h:9) nor multiples of the 128-row tile (the reference has no tail predication);
  *   - one process per GPU; a context belongs to the device that was current when it was created.
  */
 #ifndef RING_ATTENTION_B200_H_
@@ -65,8 +66,8 @@ struct Ring_fwd_params; /* csrc/ring.h of this repository: the reference's struc
  * Replaces: ring_attention(FPC* q, FPC* k, FPC* v, float* out, int npes, int mype, int* seqlen,
  *                          int dim, int max_seq)                    -- csrc/ring_attention.cu:706-722
  * Same argument order and meaning: single batch, single head, q/k/v [seqlen[mype], dim] fp16 device
- * pointers, out [seqlen[mype], dim] fp32 device pointer, seqlen a HOST array of npes entries
- * (all equal), max_seq an upper bound on them.  Non-causal.  Synchronous like the reference
+ * pointers, out [seqlen[mype], dim] fp32 device pointer, seqlen a HOST array of npes entries,
+ * max_seq an upper bound on them.  Non-causal.  Synchronous like the reference
  * (which ends in cudaDeviceSynchronize, :721).  The softmax scale is 1/sqrt(dim) in the natural
  * base (the reference's kernel applies exp2 with scale 1, csrc/ring_attention.cu:389,597, which
  * disagrees with its own PyTorch check csrc/self_attention.py:22-26; see ring_attention_scaled).

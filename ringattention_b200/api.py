@@ -170,7 +170,7 @@ class RingContext:
         check(_lib.load().ring_attention_fwd(self._h, ctypes.byref(params)), "ring_attention_fwd")
 
     def forward(self, q, k, v, out, lse=None, *, causal: bool = False, softmax_scale: Optional[float] = None,
-                stream=None, rank: Optional[int] = None) -> None:
+                stream=None, rank: Optional[int] = None, seqlens: Optional[Sequence[int]] = None) -> None:
         """q, k, v: [B, H, S_local, D] fp16/bf16 shards of this rank; out [B, H, S_local, D] fp32;
         lse [B, H, S_local] fp32 or None.  Asynchronous on `stream` (default: torch's current stream)."""
         B, H, S, D = q.shape
@@ -179,7 +179,11 @@ class RingContext:
         if lse is not None and tuple(lse.shape) != (B, H, S):
             raise ValueError("lse must be [B, H, S_local]")
         mype = self.rank if rank is None else int(rank)
-        p = set_params_fprop(q, k, v, out, self.world, mype, [S] * self.world, D, S, batch=B, heads=H, lse=lse,
+        # seqlens: rows held by every rank when the shards differ in length (the reference's seqlen[], csrc/ring.h:9)
+        table = [S] * self.world if seqlens is None else [int(x) for x in seqlens]
+        if len(table) != self.world or table[mype] != S:
+            raise ValueError("seqlens must list every rank's rows and agree with this rank's tensors")
+        p = set_params_fprop(q, k, v, out, self.world, mype, table, D, max(table), batch=B, heads=H, lse=lse,
                              causal=causal, softmax_scale=softmax_scale, stream=stream)
         self.forward_params(p)
 

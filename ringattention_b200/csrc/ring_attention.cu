@@ -611,7 +611,17 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     const int H = p.heads > 0 ? p.heads : 1;
     const int S = p.h_seqlen[r];
     const int D = p.dim;
-    const size_t shard_bytes = static_cast<size_t>(B) * H * S * D * 2;  // one of K or V
+    // Shards may differ in length (seqlen[] per PE, csrc/ring.h:9, csrc/ring_attention.cu:463,531): this rank ships
+    // `shard_bytes` of K and of V, receives bytes_of(source) of each, and every receive buffer is laid out for the
+    // longest shard (V starts at max_shard_bytes) so that sender and receiver agree without talking.
+    auto bytes_of = [&](int rank) { return static_cast<size_t>(B) * H * p.h_seqlen[rank] * D * 2; };
+    const size_t shard_bytes = bytes_of(r);  // one of K or V of this rank
+    size_t max_shard_bytes = 0;
+    std::vector<int64_t> row0(P + 1, 0);  // global index of the first row of every shard
+    for (int i = 0; i < P; ++i) {
+        max_shard_bytes = bytes_of(i) > max_shard_bytes ? bytes_of(i) : max_shard_bytes;
+        row0[i + 1] = row0[i] + p.h_seqlen[i];
+    }
     const int64_t rows = static_cast<int64_t>(B) * H * S;
     const bool causal = p.causal != 0;
     int rc;
@@ -621,12 +631,12 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     uint32_t seq = 0;
     if (peer) {
         if ((rc = stream_mem_ops(&ops))) return rc;
-        if ((rc = peer_grow_recv(c, 2 * shard_bytes))) return rc;
+        if ((rc = peer_grow_recv(c, 2 * max_shard_bytes))) return rc;
         seq = ++c->call_seq;
     } else {
         if (c->recv_block) return fail(RING_ERR_UNSUPPORTED, "switching from the peer-copy transport back to NCCL is not supported");
-        if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * shard_bytes))) return rc;
-        if (P > 2 && (rc = grow(&c->recv[1], &c->recv_cap[1], 2 * shard_bytes))) return rc;
+        if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * max_shard_bytes))) return rc;
+        if (P > 2 && (rc = grow(&c->recv[1], &c->recv_cap[1], 2 * max_shard_bytes))) return rc;
     }
     float* lse = static_cast<float*>(p.lse_ptr);
     if (!lse) {
@@ -675,22 +685,23 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             if (s >= 2 && !peer) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
             if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_comm_start[s], c->comm_stream));
             char* dst_k = static_cast<char*>(c->recv[plan.recv_buffer]);
-            char* dst_v = dst_k + shard_bytes;
+            char* dst_v = dst_k + max_shard_bytes;
+            const size_t in_bytes = bytes_of(nsrc);
             if (peer) {
                 if (do_send) {
                     CUstream cs = reinterpret_cast<CUstream>(c->comm_stream);
                     RING_CU(ops.wait(cs, reinterpret_cast<CUdeviceptr>(c->flags + kFlagCredit + s), seq, CU_STREAM_WAIT_VALUE_GEQ));
                     char* remote = static_cast<char*>(c->peer_recv_block[ndst]) + plan.recv_buffer * c->peer_recv_half[ndst];
                     RING_CUDA(cudaMemcpyAsync(remote, p.k_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
-                    RING_CUDA(cudaMemcpyAsync(remote + shard_bytes, p.v_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                    RING_CUDA(cudaMemcpyAsync(remote + max_shard_bytes, p.v_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                     RING_CU(ops.write(cs, reinterpret_cast<CUdeviceptr>(c->peer_flags[ndst] + kFlagReady + s), seq, 0));
                 }
             } else if (c->local) {
                 if (do_recv) {
                     if (!c->local_k[nsrc] || !c->local_v[nsrc])
                         return fail(RING_ERR_INVALID_ARGUMENT, "local shard %d was not registered", nsrc);
-                    RING_CUDA(cudaMemcpyAsync(dst_k, c->local_k[nsrc], shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
-                    RING_CUDA(cudaMemcpyAsync(dst_v, c->local_v[nsrc], shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                    RING_CUDA(cudaMemcpyAsync(dst_k, c->local_k[nsrc], in_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
+                    RING_CUDA(cudaMemcpyAsync(dst_v, c->local_v[nsrc], in_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                 }
             } else if (do_recv || do_send) {
                 NcclApi& n = nccl();
@@ -700,8 +711,8 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
                     RING_NCCL(n.Send(p.v_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream));
                 }
                 if (do_recv) {
-                    RING_NCCL(n.Recv(dst_k, shard_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
-                    RING_NCCL(n.Recv(dst_v, shard_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
+                    RING_NCCL(n.Recv(dst_k, in_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
+                    RING_NCCL(n.Recv(dst_v, in_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
                 }
                 RING_NCCL(n.GroupEnd());
             }
@@ -726,16 +737,16 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             BlockLaunch L;
             L.q = p.q_ptr;
             L.k = plan.compute_buffer < 0 ? p.k_ptr : c->recv[plan.compute_buffer];
-            L.v = plan.compute_buffer < 0 ? p.v_ptr : static_cast<char*>(c->recv[plan.compute_buffer]) + shard_bytes;
+            L.v = plan.compute_buffer < 0 ? p.v_ptr : static_cast<char*>(c->recv[plan.compute_buffer]) + max_shard_bytes;
             L.batch = B;
             L.heads = H;
             L.sq = S;
-            L.sk = S;
+            L.sk = p.h_seqlen[src];
             L.dim = D;
             L.scale = p.softmax_scale;
             L.causal = causal;
-            L.q_off = static_cast<int64_t>(r) * S;
-            L.k_off = static_cast<int64_t>(src) * S;
+            L.q_off = row0[r];
+            L.k_off = row0[src];
             L.is_bf16 = p.is_bf16;
             if (!have_partial || c->merge_mode == RING_MERGE_FUSED_EPILOGUE) {
                 L.o = static_cast<float*>(p.out_ptr);
@@ -786,11 +797,8 @@ int validate_params(RingCtx* c, const Ring_fwd_params* p) {
     if (p->dim != 64 && p->dim != 128) return fail(RING_ERR_INVALID_ARGUMENT, "dim must be 64 or 128, got %d", p->dim);
     if (!p->h_seqlen) return fail(RING_ERR_INVALID_ARGUMENT, "params.h_seqlen (host sequence-length table) is null");
     for (int i = 0; i < p->npes; ++i)
-        if (p->h_seqlen[i] != p->h_seqlen[0])
-            return fail(RING_ERR_INVALID_ARGUMENT, "uneven shards are not supported (seqlen[%d] = %d, seqlen[0] = %d)", i,
-                        p->h_seqlen[i], p->h_seqlen[0]);
-    if (p->h_seqlen[0] <= 0)
-        return fail(RING_ERR_INVALID_ARGUMENT, "seqlen per rank must be positive, got %d", p->h_seqlen[0]);
+        if (p->h_seqlen[i] <= 0 || p->h_seqlen[i] > (1 << 24))
+            return fail(RING_ERR_INVALID_ARGUMENT, "seqlen[%d] = %d: every rank needs between 1 and 2^24 rows", i, p->h_seqlen[i]);
     if (!(p->softmax_scale > 0.f) || !std::isfinite(p->softmax_scale))
         return fail(RING_ERR_INVALID_ARGUMENT, "softmax_scale must be positive and finite");
     int dev = -1;

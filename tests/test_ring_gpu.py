@@ -75,6 +75,31 @@ def test_virtual_ring_ragged_shard_length(ra):
         assert_parity(o, lse, want_o, want_lse, f"ragged ring causal={causal}")
 
 
+@pytest.mark.parametrize("causal", [False, True])
+def test_virtual_ring_uneven_shards(ra, causal):
+    """Per-rank sequence lengths that differ (the reference's seqlen[] table, csrc/ring.h:9, :463,531)."""
+    import torch
+    B, H, D = 1, 2, 128
+    lens = [384, 130, 512, 257]
+    S, world = sum(lens), len(lens)
+    q, k, v = synthetic.make_qkv(7373, B, H, D, 0, S)
+    starts = np.concatenate([[0], np.cumsum(lens)])
+    sh = lambda x: [to_dev(x[:, :, starts[r]:starts[r + 1]]) for r in range(world)]
+    qs, ks, vs = sh(q), sh(k), sh(v)
+    ctx = ra.RingContext.create_local(world)
+    ctx.set_local_shards(ks, vs)
+    outs, lses = [], []
+    for r in range(world):
+        out = torch.full((B, H, lens[r], D), float("nan"), device="cuda")
+        lse = torch.full((B, H, lens[r]), float("nan"), device="cuda")
+        ctx.forward(qs[r], ks[r], vs[r], out, lse, causal=causal, rank=r, seqlens=lens)
+        outs.append(out); lses.append(lse)
+    ctx.synchronize()
+    ctx.destroy()
+    want_o, want_lse = oracle.attention_fwd(q, k, v, D ** -0.5, causal)
+    assert_parity(torch.cat(outs, 2).cpu().numpy(), torch.cat(lses, 2).cpu().numpy(), want_o, want_lse, "uneven shards")
+
+
 def test_context_rejects_mismatched_calls(ra):
     import torch
     ctx = ra.RingContext.create_local(2)
@@ -86,8 +111,8 @@ def test_context_rejects_mismatched_calls(ra):
     p = ra.set_params_fprop(x, x, x, out, 3, 0, [128, 128, 128], 64)
     with pytest.raises(ra.RingError):               # npes differs from the context's world
         ctx.forward_params(p)
-    p = ra.set_params_fprop(x, x, x, out, 2, 0, [128, 256], 64)
-    with pytest.raises(ra.RingError):               # uneven shards
+    p = ra.set_params_fprop(x, x, x, out, 2, 0, [128, 0], 64)
+    with pytest.raises(ra.RingError):               # a rank without rows
         ctx.forward_params(p)
     ctx.destroy()
 
