@@ -126,7 +126,8 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int warp = tid >> 5;
     const int lane = tid & 31;
 
-    const int r0 = blockIdx.x * T::kBlockM;  // first Q row of this CTA
+    // Under a causal mask the CTAs of the last Q rows have the most K/V blocks to visit: launch them first.
+    const int r0 = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * T::kBlockM;  // first Q row of this CTA
     const bool tile1_valid = (r0 + 128) < a.sq;
     const int ntiles = tile1_valid ? 2 : 1;
 
