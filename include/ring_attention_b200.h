@@ -50,6 +50,10 @@ struct Ring_fwd_params; /* csrc/ring.h of this repository: the reference's struc
 #define RING_OPT_CAUSAL_SKIP_EXCHANGE 2 /* 1 (default): under a causal mask, do not ship shards nobody will read */
 #define RING_OPT_RECORD_TIMINGS 3       /* 1: record per-step events so ring_ctx_get_timings() works */
 #define RING_OPT_TRANSPORT 4            /* how K/V shards travel between ranks, see below */
+#define RING_OPT_CAUSAL_ZIGZAG 5        /* 1: causal calls assume zig-zag sharding: the sequence is cut into 2*npes chunks
+                                           and rank r holds chunks r and 2*npes-1-r, in that order, in its q/k/v/out/lse.
+                                           Contiguous causal sharding (the default) makes rank r do (r + 1/2) / npes of the
+                                           work; zig-zag gives every rank the same.  Needs equal, even shard lengths. */
 
 /* Transports of the K/V exchange.  Both keep the same schedule (ring_step_plan) and the same double buffer.
  *   NCCL:      ncclSend/ncclRecv on the exchange stream (what the reference's NCCL prototype does,

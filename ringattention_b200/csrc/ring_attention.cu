@@ -166,14 +166,16 @@ int encode_fn(EncodeTiledFn* out) {
 // [batch, heads, rows, dim] 16-bit tensor -> 4-D map, box = 64 x 128 x 1 x 1 elements, 128-byte swizzle.
 // Out-of-range rows read as zero, which gives tail predication for free (the reference has none and
 // needs seqlen % 64 == 0, csrc/ring_attention.cu:131,143-145).
-int make_tensor_map(CUtensorMap* tm, const void* base, int batch, int heads, int rows, int dim, bool bf16) {
+int make_tensor_map(CUtensorMap* tm, const void* base, int batch, int heads, int rows, int dim, bool bf16,
+                    int64_t rows_total = 0) {
+    if (rows_total <= 0) rows_total = rows;  // rows_total > rows: `base` points at a row range inside longer (b, h) slabs
     EncodeTiledFn enc = nullptr;
     int rc = encode_fn(&enc);
     if (rc) return rc;
     const cuuint64_t dims[4] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(rows),
                                 static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(rows) * dim * 2,
-                                   static_cast<cuuint64_t>(heads) * rows * dim * 2};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(rows_total) * dim * 2,
+                                   static_cast<cuuint64_t>(heads) * rows_total * dim * 2};
     const cuuint32_t box[4] = {64, 128, 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
@@ -229,6 +231,8 @@ struct BlockLaunch {
     int64_t q_off, k_off;
     int merge;
     int is_bf16;
+    // > 0: q/o/lse (k/v) point at a row range inside (batch, head) slabs of this many rows
+    int64_t q_rows_total = 0, k_rows_total = 0;
 };
 
 template <class Traits>
@@ -241,18 +245,19 @@ int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t st
     }
     CUtensorMap tq, tk, tv;
     int rc;
-    if ((rc = make_tensor_map(&tq, L.q, L.batch, L.heads, L.sq, L.dim, L.is_bf16))) return rc;
-    if ((rc = make_tensor_map(&tk, L.k, L.batch, L.heads, L.sk, L.dim, L.is_bf16))) return rc;
-    if ((rc = make_tensor_map(&tv, L.v, L.batch, L.heads, L.sk, L.dim, L.is_bf16))) return rc;
+    if ((rc = make_tensor_map(&tq, L.q, L.batch, L.heads, L.sq, L.dim, L.is_bf16, L.q_rows_total))) return rc;
+    if ((rc = make_tensor_map(&tk, L.k, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
+    if ((rc = make_tensor_map(&tv, L.v, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
+    const int64_t q_slab = L.q_rows_total > 0 ? L.q_rows_total : L.sq;
 
     ring::BlockFwdArgs a;
     a.o = L.o;
     a.lse = L.lse;
     a.o_row_stride = L.dim;
-    a.o_head_stride = static_cast<int64_t>(L.sq) * L.dim;
+    a.o_head_stride = q_slab * L.dim;
     a.o_batch_stride = a.o_head_stride * L.heads;
-    a.lse_head_stride = L.sq;
-    a.lse_batch_stride = static_cast<int64_t>(L.sq) * L.heads;
+    a.lse_head_stride = q_slab;
+    a.lse_batch_stride = q_slab * L.heads;
     a.heads = L.heads;
     a.sq = L.sq;
     a.sk = L.sk;
@@ -370,6 +375,7 @@ struct RingCtx {
     size_t o_part_cap = 0, lse_part_cap = 0, lse_own_cap = 0;  // bytes
     int merge_mode = RING_MERGE_FUSED_EPILOGUE;
     int causal_skip = 1;
+    int zigzag = 0;  // causal sharding: 0 contiguous, 1 zig-zag (rank r holds half-chunks r and 2P-1-r)
     int record_timings = 0;
     int last_steps = 0;
     bool step_computed[kMaxWorld] = {};
@@ -625,6 +631,15 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     const int64_t rows = static_cast<int64_t>(B) * H * S;
     const bool causal = p.causal != 0;
     int rc;
+    // Zig-zag causal sharding: the sequence is cut into 2P chunks and rank r holds chunks r and 2P-1-r (in that order),
+    // so that every rank masks the same amount.  Every step then has visible keys and every shard travels.
+    const bool zig = causal && c->zigzag;
+    const int plan_causal = (causal && !zig) ? 1 : 0;
+    if (zig) {
+        for (int i = 0; i < P; ++i)
+            if (p.h_seqlen[i] != S || (S & 1))
+                return fail(RING_ERR_INVALID_ARGUMENT, "zig-zag sharding needs equal, even shard lengths");
+    }
 
     const bool peer = !c->local && P > 1 && c->transport == RING_TRANSPORT_PEER_COPY;
     StreamMemOps ops;
@@ -660,7 +675,7 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         // origins of the first two exchanges.
         for (int e = 0; e < 2 && e < P - 1; ++e) {
             RingStepPlan pe;
-            if ((rc = ring_step_plan(P, r, e, causal ? 1 : 0, c->causal_skip, &pe))) return rc;
+            if ((rc = ring_step_plan(P, r, e, plan_causal, c->causal_skip, &pe))) return rc;
             if (pe.do_recv)
                 RING_CU(ops.write(reinterpret_cast<CUstream>(stream),
                                   reinterpret_cast<CUdeviceptr>(c->peer_flags[pe.recv_from] + kFlagCredit + e), seq, 0));
@@ -669,10 +684,11 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
 
     c->last_steps = P;
     bool have_partial = false;
+    bool zig_have[2] = {false, false};
     bool prev_do_recv = false;
     for (int s = 0; s < P; ++s) {
         RingStepPlan plan;
-        if ((rc = ring_step_plan(P, r, s, causal ? 1 : 0, c->causal_skip, &plan))) return rc;
+        if ((rc = ring_step_plan(P, r, s, plan_causal, c->causal_skip, &plan))) return rc;
         const int src = plan.src_rank;
 
         // ---- exchange s: bring the shard of step s + 1 into recv[s & 1] while step s computes --------
@@ -733,7 +749,36 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_compute_start[s], stream));
         const bool compute = plan.compute != 0;
         c->step_computed[s] = compute;
-        if (compute) {
+        if (compute && zig) {
+            // four half-shard products per step, of which the causal mask leaves two (three on the own shard)
+            const int half = S / 2;
+            const char* kbase = static_cast<const char*>(plan.compute_buffer < 0 ? p.k_ptr : c->recv[plan.compute_buffer]);
+            const char* vbase = plan.compute_buffer < 0 ? static_cast<const char*>(p.v_ptr)
+                                                        : static_cast<const char*>(c->recv[plan.compute_buffer]) + max_shard_bytes;
+            for (int qp = 0; qp < 2; ++qp) {
+                for (int kp = 0; kp < 2; ++kp) {
+                    const int q_chunk = qp ? 2 * P - 1 - r : r;
+                    const int k_chunk = kp ? 2 * P - 1 - src : src;
+                    if (k_chunk > q_chunk) continue;  // every key after every query
+                    BlockLaunch L;
+                    L.q = static_cast<const char*>(p.q_ptr) + static_cast<size_t>(qp) * half * D * 2;
+                    L.k = kbase + static_cast<size_t>(kp) * half * D * 2;
+                    L.v = vbase + static_cast<size_t>(kp) * half * D * 2;
+                    L.o = static_cast<float*>(p.out_ptr) + static_cast<size_t>(qp) * half * D;
+                    L.lse = lse + static_cast<size_t>(qp) * half;
+                    L.batch = B; L.heads = H; L.sq = half; L.sk = half; L.dim = D;
+                    L.q_rows_total = S; L.k_rows_total = S;
+                    L.scale = p.softmax_scale;
+                    L.causal = k_chunk == q_chunk;  // only the diagonal chunk pair is masked inside
+                    L.q_off = static_cast<int64_t>(q_chunk) * half;
+                    L.k_off = static_cast<int64_t>(k_chunk) * half;
+                    L.is_bf16 = p.is_bf16;
+                    L.merge = zig_have[qp] ? 1 : 0;
+                    if ((rc = launch_block(L, stream))) return rc;
+                    zig_have[qp] = true;
+                }
+            }
+        } else if (compute) {
             BlockLaunch L;
             L.q = p.q_ptr;
             L.k = plan.compute_buffer < 0 ? p.k_ptr : c->recv[plan.compute_buffer];
@@ -767,7 +812,7 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         if (peer && s >= 1 && s + 1 <= P - 2) {
             // step s was the last reader of receive buffer (s - 1) & 1 = (s + 1) & 1: free it for exchange s + 1
             RingStepPlan pe;
-            if ((rc = ring_step_plan(P, r, s + 1, causal ? 1 : 0, c->causal_skip, &pe))) return rc;
+            if ((rc = ring_step_plan(P, r, s + 1, plan_causal, c->causal_skip, &pe))) return rc;
             if (pe.do_recv)
                 RING_CU(ops.write(reinterpret_cast<CUstream>(stream),
                                   reinterpret_cast<CUdeviceptr>(c->peer_flags[pe.recv_from] + kFlagCredit + s + 1), seq, 0));
@@ -933,6 +978,9 @@ int ring_ctx_set_option(RingCtx* ctx, int option, int value) {
         case RING_OPT_RECORD_TIMINGS:
             ctx->record_timings = value ? 1 : 0;
             return RING_OK;
+        case RING_OPT_CAUSAL_ZIGZAG:
+            ctx->zigzag = value ? 1 : 0;
+            return RING_OK;
         case RING_OPT_TRANSPORT:
             if (value != RING_TRANSPORT_NCCL && value != RING_TRANSPORT_PEER_COPY)
                 return fail(RING_ERR_INVALID_ARGUMENT, "bad transport %d", value);
@@ -952,6 +1000,7 @@ int ring_ctx_get_option(RingCtx* ctx, int option, int* value) {
         case RING_OPT_CAUSAL_SKIP_EXCHANGE: *value = ctx->causal_skip; return RING_OK;
         case RING_OPT_RECORD_TIMINGS: *value = ctx->record_timings; return RING_OK;
         case RING_OPT_TRANSPORT: *value = ctx->transport; return RING_OK;
+        case RING_OPT_CAUSAL_ZIGZAG: *value = ctx->zigzag; return RING_OK;
         default: return fail(RING_ERR_INVALID_ARGUMENT, "unknown option %d", option);
     }
 }

@@ -77,3 +77,12 @@ def make_head(which: str, seed: int, H: int, D: int, b: int, h: int, row_start: 
         hi = min(g0 + ROW_BLOCK, row_start + rows)
         out[lo - row_start:hi - row_start, :] = vals[lo - g0:hi - g0, :]
     return out
+
+
+def zigzag_rows(rank: int, world: int, S: int) -> np.ndarray:
+    """Global row indices held by `rank` under zig-zag sharding: the sequence of S rows is cut into 2 * world
+    chunks and the rank holds chunk `rank` followed by chunk `2 * world - 1 - rank`."""
+    chunk = S // (2 * world)
+    a = np.arange(rank * chunk, (rank + 1) * chunk)
+    b = np.arange((2 * world - 1 - rank) * chunk, (2 * world - rank) * chunk)
+    return np.concatenate([a, b])

@@ -24,6 +24,8 @@ CONFIGS = {
     "c2": (2, 2, 16, 8192, 128, False, 1.0, 3, 64),
     "c3": (4, 1, 32, 32768, 128, False, 0.5, 3, 64),
     "c4": (8, 1, 32, 131072, 128, True, 1.0, 2, 48),
+    "c4_zigzag": (8, 1, 32, 131072, 128, True, 1.0, 2, 48),     # same problem, zig-zag sharding
+    "small_zigzag": (None, 1, 4, None, 128, True, 1.0, 2, 48),  # S_total = 512 * world
     "c5": (8, 1, 8, 1048576, 128, False, 1.0, 1, 24),
 }
 
@@ -51,13 +53,21 @@ def main():
     if cw is not None and cw != world:
         raise SystemExit(f"config {args.config} needs world {cw}, got {world}")
     if S is None:
-        S = (512 if args.config == "small" else 256) * world
+        S = (256 if args.config == "small_causal" else 512) * world
+    zigzag = args.config.endswith("zigzag")
     Sl = S // world
     seed = 4321
     scale = D ** -0.5
 
     t0 = time.time()
-    q, k, v = (torch.from_numpy(x).to(dev) for x in synthetic.make_qkv(seed, B, H, D, rank * Sl, Sl, gain))
+    if zigzag:  # this rank's rows: chunk `rank` then chunk `2 * world - 1 - rank`
+        my_rows = synthetic.zigzag_rows(rank, world, S)
+        ch = Sl // 2
+        parts = [synthetic.make_qkv(seed, B, H, D, int(my_rows[0]), ch, gain), synthetic.make_qkv(seed, B, H, D, int(my_rows[ch]), ch, gain)]
+        q, k, v = (torch.from_numpy(np.concatenate([parts[0][i], parts[1][i]], axis=2)).to(dev) for i in range(3))
+    else:
+        my_rows = np.arange(rank * Sl, (rank + 1) * Sl)
+        q, k, v = (torch.from_numpy(x).to(dev) for x in synthetic.make_qkv(seed, B, H, D, rank * Sl, Sl, gain))
     t_gen = time.time() - t0
     out = torch.full((B, H, Sl, D), float("nan"), device=dev)
     lse = torch.full((B, H, Sl), float("nan"), device=dev)
@@ -67,6 +77,7 @@ def main():
     transport = "peer" if ctx.get_option(ra.RING_OPT_TRANSPORT) == ra.RING_TRANSPORT_PEER_COPY else "nccl"
     ctx.set_option(ra.RING_OPT_MERGE_MODE, args.merge_mode)
     ctx.set_option(ra.RING_OPT_RECORD_TIMINGS, 1)
+    ctx.set_option(ra.RING_OPT_CAUSAL_ZIGZAG, int(zigzag))
     for _ in range(3):
         out.fill_(float("nan")); lse.fill_(float("nan"))
         ctx.forward(q, k, v, out, lse, causal=causal, softmax_scale=scale)
@@ -87,7 +98,14 @@ def main():
         vf = synthetic.make_head("v", seed, H, D, b, h, 0, S, gain)[None, None]
         qh = np.ascontiguousarray(q[b, h].cpu().numpy())[None, None]
         rows = np.stack([np.zeros_like(idx), np.zeros_like(idx), idx], axis=1)
-        want_o, want_l = oracle.attention_rows(qh, kf, vf, rows, scale, causal, q_off=rank * Sl, k_off=0)
+        # global index of local row i: my_rows[i] (one run of rows, or two under zig-zag sharding)
+        want_o = np.empty((len(idx), D), np.float32); want_l = np.empty(len(idx), np.float32)
+        cut = Sl // 2
+        for part in (0, 1):
+            sel = (idx >= cut) if part else (idx < cut)
+            if sel.any():
+                off = int(my_rows[part * cut]) - part * cut
+                want_o[sel], want_l[sel] = oracle.attention_rows(qh, kf, vf, rows[sel], scale, causal, q_off=off, k_off=0)
         got_o, got_l = o_host[b, h, idx], l_host[b, h, idx]
         err_o = max(err_o, float(np.abs(got_o - want_o).max()))
         err_l = max(err_l, float(np.abs(got_l - want_l).max()))

@@ -100,6 +100,35 @@ def test_virtual_ring_uneven_shards(ra, causal):
     assert_parity(torch.cat(outs, 2).cpu().numpy(), torch.cat(lses, 2).cpu().numpy(), want_o, want_lse, "uneven shards")
 
 
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_virtual_ring_zigzag_causal(ra, world):
+    """Zig-zag causal sharding: rank r holds chunks r and 2P-1-r; the result, put back in sequence order, is
+    plain causal attention."""
+    import torch
+    B, H, D = 1, 2, 128
+    S = 512 * world
+    q, k, v = synthetic.make_qkv(8800 + world, B, H, D, 0, S)
+    rows = [synthetic.zigzag_rows(r, world, S) for r in range(world)]
+    sh = lambda x: [to_dev(x[:, :, rows[r]]) for r in range(world)]
+    qs, ks, vs = sh(q), sh(k), sh(v)
+    ctx = ra.RingContext.create_local(world)
+    ctx.set_option(ra.RING_OPT_CAUSAL_ZIGZAG, 1)
+    ctx.set_local_shards(ks, vs)
+    got_o = np.empty((B, H, S, D), np.float32); got_l = np.empty((B, H, S), np.float32)
+    outs = []
+    for r in range(world):
+        out = torch.full((B, H, S // world, D), float("nan"), device="cuda")
+        lse = torch.full((B, H, S // world), float("nan"), device="cuda")
+        ctx.forward(qs[r], ks[r], vs[r], out, lse, causal=True, rank=r)
+        outs.append((out, lse))
+    ctx.synchronize()
+    for r in range(world):
+        got_o[:, :, rows[r]] = outs[r][0].cpu().numpy(); got_l[:, :, rows[r]] = outs[r][1].cpu().numpy()
+    ctx.destroy()
+    want_o, want_lse = oracle.attention_fwd(q, k, v, D ** -0.5, True)
+    assert_parity(got_o, got_l, want_o, want_lse, f"zig-zag world={world}")
+
+
 def test_context_rejects_mismatched_calls(ra):
     import torch
     ctx = ra.RingContext.create_local(2)

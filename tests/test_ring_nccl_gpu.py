@@ -48,7 +48,14 @@ def test_ring_small(world, config, merge_mode, transport, tmp_path):
     assert r["transport"] == transport
 
 
-@pytest.mark.parametrize("config,world", [("c2", 2), ("c3", 4), ("c4", 8), ("c5", 8)])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_ring_small_zigzag(world, tmp_path):
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    _run(world, "small_zigzag", 1, tmp_path)
+
+
+@pytest.mark.parametrize("config,world", [("c2", 2), ("c3", 4), ("c4", 8), ("c4_zigzag", 8), ("c5", 8)])
 def test_nccl_ring_baseline_configs(config, world, tmp_path):
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
