@@ -214,6 +214,15 @@ int ring_attention_chunked_fwd_static(const void* q, const void* k, const void* 
 int ring_device_status(int* status_out);
 int ring_device_status_reset(void);
 
+/*
+ * Failure detection without a device fault.  ring_device_status_inject stores a code in the status word from the
+ * host, as a timed-out kernel would; ring_selftest_wait_timeout runs the kernels' bounded wait on a barrier that
+ * nothing completes and returns what it recorded and how long it waited (about two seconds).  No counterpart in
+ * the reference, whose device code can only hang (its grid barrier is commented out, csrc/ring_attention.cu:457-459).
+ */
+int ring_device_status_inject(int code);
+int ring_selftest_wait_timeout(int code, int* status_out, float* waited_ms);
+
 /* Number of kernels this library has launched in this process (block + merge), for accounting. */
 int64_t ring_kernel_launch_count(void);
 

@@ -73,6 +73,8 @@ SYMBOLS = {
                                                   c_float, c_int, c_int, c_int, c_void_p]),
     "ring_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "ring_device_status_reset": (c_int, []),
+    "ring_device_status_inject": (c_int, [c_int]),
+    "ring_selftest_wait_timeout": (c_int, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_float)]),
     "ring_kernel_launch_count": (c_int64, []),
     "ring_last_error_string": (ctypes.c_char_p, []),
 }

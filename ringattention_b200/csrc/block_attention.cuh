@@ -507,4 +507,19 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     }
 }
 
+// One warp waits, with the same bounded wait the block kernel uses, on an mbarrier that nobody arrives at.
+// It must come back after the limit with `code` in the status word (used by the library's self-test).
+__global__ void ring_wait_timeout_probe(int* status, int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        ptx::fence_mbar_init();
+    }
+    __syncwarp();
+    const bool ok = ptx::mbar_wait(ptx::smem_u32(&bar), 0, &abort_flag, status, code);
+    if (ok && threadIdx.x == 0) atomicCAS(status, 0, -1);  // the wait must NOT have succeeded
+}
+
 }  // namespace ring

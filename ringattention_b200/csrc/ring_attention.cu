@@ -876,6 +876,42 @@ int ring_device_status_reset(void) {
     return RING_OK;
 }
 
+// Host-side fault injection for tests: stores `code` in the device status word, as a kernel whose bounded wait
+// ran out would.  Every later kernel of this library then returns at once until ring_device_status_reset().
+int ring_device_status_inject(int code) {
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    RING_CUDA(cudaDeviceSynchronize());
+    RING_CUDA(cudaMemcpy(st->d_status, &code, sizeof(int), cudaMemcpyHostToDevice));
+    return RING_OK;
+}
+
+// Runs the kernels' bounded wait on an mbarrier that nothing ever completes (one CTA, one thread) and reports what
+// it left in `status_out`: the wait must give up after its limit (about two seconds), record `code`, and return.
+int ring_selftest_wait_timeout(int code, int* status_out, float* waited_ms) {
+    if (!status_out) return fail(RING_ERR_INVALID_ARGUMENT, "null status_out");
+    int* d = nullptr;
+    RING_CUDA(cudaMalloc(&d, sizeof(int)));
+    RING_CUDA(cudaMemset(d, 0, sizeof(int)));
+    cudaEvent_t e0, e1;
+    RING_CUDA(cudaEventCreate(&e0));
+    RING_CUDA(cudaEventCreate(&e1));
+    RING_CUDA(cudaEventRecord(e0, 0));
+    ring::ring_wait_timeout_probe<<<1, 32>>>(d, code);
+    RING_CUDA(cudaGetLastError());
+    RING_CUDA(cudaEventRecord(e1, 0));
+    RING_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    RING_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    if (waited_ms) *waited_ms = ms;
+    RING_CUDA(cudaMemcpy(status_out, d, sizeof(int), cudaMemcpyDeviceToHost));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    RING_CUDA(cudaFree(d));
+    return RING_OK;
+}
+
 int ring_get_unique_id(void* id_out) {
     if (!id_out) return fail(RING_ERR_INVALID_ARGUMENT, "null id_out");
     NcclApi& n = nccl();
