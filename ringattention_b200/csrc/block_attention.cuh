@@ -79,9 +79,6 @@ struct BlockFwdArgs {
 
 constexpr float kRescaleThresholdLog2 = 8.0f;
 
-#ifndef RING_USE_MAX3
-#define RING_USE_MAX3 1  // three-input max.f32 in the row-maximum reduction
-#endif
 #ifndef RING_PV_AFTER_QK
 #define RING_PV_AFTER_QK 0
 #endif
@@ -353,23 +350,16 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 }
 
                 // row maximum of the block; adopt it only when it beats the one in use by more than 2^8
-#if RING_USE_MAX3
-                float mx0 = fmax3(s[0], s[1], s[2]), mx1 = fmax3(s[3], s[4], s[5]);
+                // eight independent chains (a chain of dependent max instructions is latency bound), then a tree
+                float mxc[8];
 #pragma unroll
-                for (int i = 6; i + 3 < 128; i += 4) {
-                    mx0 = fmax3(mx0, s[i], s[i + 1]);
-                    mx1 = fmax3(mx1, s[i + 2], s[i + 3]);
-                }
-                const float mx = fmax3(mx0, mx1, fmaxf(s[126], s[127]));
-#else
-                float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+                for (int u = 0; u < 8; ++u) mxc[u] = fmaxf(s[2 * u], s[2 * u + 1]);
 #pragma unroll
-                for (int i = 4; i < 128; i += 4) {
-                    mx0 = fmaxf(mx0, s[i]); mx1 = fmaxf(mx1, s[i + 1]);
-                    mx2 = fmaxf(mx2, s[i + 2]); mx3 = fmaxf(mx3, s[i + 3]);
+                for (int i = 16; i < 128; i += 16) {
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) mxc[u] = fmax3(mxc[u], s[i + 2 * u], s[i + 2 * u + 1]);
                 }
-                const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-#endif
+                const float mx = fmaxf(fmax3(mxc[0], mxc[1], mxc[2]), fmax3(fmax3(mxc[3], mxc[4], mxc[5]), mxc[6], mxc[7]));
                 float alpha = 1.f;  // factor owed to everything accumulated before this block
                 if (mx > m_run && (m_run == -INFINITY || (mx - m_run) * c > kRescaleThresholdLog2)) {
                     alpha = (m_run == -INFINITY) ? 0.f : ex2_approx((m_run - mx) * c);
