@@ -73,8 +73,10 @@ struct BlockFwdArgs {
 
 #ifdef RING_TRACE
 #define RING_TRACE_STAMP(cond, slot) do { if ((cond) && a.trace && blockIdx.x == 0 && blockIdx.y == 0) a.trace[j * 32 + (slot)] = clock64(); } while (0)
+#define RING_TRACE_LIFE(cond, k) do { if ((cond) && a.trace) { const int w_ = (blockIdx.x == 0 && blockIdx.y == 0) ? 0 : ((blockIdx.x == 16 && blockIdx.y == 20) ? 1 : -1); if (w_ >= 0) a.trace[((a.sk + 127) / 128) * 32 + 16 * w_ + (k)] = clock64(); } } while (0)
 #else
 #define RING_TRACE_STAMP(cond, slot) do { } while (0)
+#define RING_TRACE_LIFE(cond, k) do { } while (0)
 #endif
 
 constexpr float kRescaleThresholdLog2 = 8.0f;
@@ -122,6 +124,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    RING_TRACE_LIFE(tid == 0, 0);
 
     // Under a causal mask the CTAs of the last Q rows have the most K/V blocks to visit: launch them first.
     const int r0 = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * T::kBlockM;  // first Q row of this CTA
@@ -160,6 +163,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     __syncthreads();
     tcgen05_fence_after_thread_sync();
     const uint32_t tmem_base = *tmem_slot;
+    RING_TRACE_LIFE(tid == 0, 1);
 
     // ---- work assignment --------------------------------------------------------------------------
     const int bh = blockIdx.y;
@@ -326,6 +330,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 0);
+                RING_TRACE_LIFE(tid == 0 && j == 0, 2);
                 tcgen05_fence_after_thread_sync();
 #pragma unroll
                 for (int i = 0; i < 4; ++i)
@@ -424,6 +429,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 5);
             }
 
+            RING_TRACE_LIFE(tid == 0, 3);
             // ---- epilogue: O / l, LSE, optional fold into an earlier partial -----------------------
             if (ok && nblk > 0) {
                 ok = mbar_wait(bar_o_done(t), (nblk - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
@@ -437,7 +443,6 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 float w_old = 0.f;
                 const bool row_ok = row < a.sq;
                 float* lse_ptr = a.lse + b * a.lse_batch_stride + h * a.lse_head_stride + row;
-                float* o_ptr = a.o + b * a.o_batch_stride + h * a.o_head_stride + static_cast<int64_t>(row) * a.o_row_stride;
                 if (a.merge && row_ok) {
                     const float lse_old = *lse_ptr;
                     const float mx = fmaxf(lse_old, lse_new);
@@ -453,41 +458,65 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         lse_new = mx + logf(tot);
                     }
                 }
+                // O goes out through shared memory so that every store instruction writes whole rows: the Q tile of
+                // this warpgroup is free (its last S product has been read), each warp stages its 32 rows there, half
+                // of the columns at a time, in 16-byte chunks XOR-swizzled by the row (conflict-free both ways).
+                constexpr int kHalfCols = D / 2;              // columns per pass
+                constexpr int kChunks = kHalfCols / 4;        // 16-byte chunks per staged row
+                constexpr int kRowsPerInst = 32 / kChunks;    // rows one coalesced instruction covers
+                const uint32_t stage = smem_q(t) + static_cast<uint32_t>(quarter) * (kTileBytes / 4);
+                const int row_base = r0 + t * 128 + quarter * 32;
+                float* o_base = a.o + b * a.o_batch_stride + h * a.o_head_stride;
+#pragma unroll 1
+                for (int pass = 0; pass < 2; ++pass) {
 #pragma unroll
-                for (int i = 0; i < D / 32; ++i) {
-                    uint32_t orr[32];
-                    if (nblk > 0) {
-                        tmem_ld_x32(t_o + 32 * i, orr);
-                        tmem_wait_ld();
-                    } else {
+                    for (int i = 0; i < kHalfCols / 32; ++i) {
+                        uint32_t orr[32];
+                        if (nblk > 0) {
+                            tmem_ld_x32(t_o + pass * kHalfCols + 32 * i, orr);
+                            tmem_wait_ld();
+                        } else {
 #pragma unroll
-                        for (int x = 0; x < 32; ++x) orr[x] = 0u;
-                    }
-                    if (row_ok) {
-                        float4* dst = reinterpret_cast<float4*>(o_ptr + 32 * i);
+                            for (int x = 0; x < 32; ++x) orr[x] = 0u;
+                        }
 #pragma unroll
                         for (int x = 0; x < 8; ++x) {
-                            float4 val;
-                            val.x = __uint_as_float(orr[4 * x + 0]) * w_new;
-                            val.y = __uint_as_float(orr[4 * x + 1]) * w_new;
-                            val.z = __uint_as_float(orr[4 * x + 2]) * w_new;
-                            val.w = __uint_as_float(orr[4 * x + 3]) * w_new;
-                            if (a.merge) {
-                                const float4 old = dst[x];
-                                val.x = fmaf(old.x, w_old, val.x);
-                                val.y = fmaf(old.y, w_old, val.y);
-                                val.z = fmaf(old.z, w_old, val.z);
-                                val.w = fmaf(old.w, w_old, val.w);
-                            }
-                            dst[x] = val;
+                            const int chunk = i * 8 + x;
+                            st_shared_v4(stage + lane * (kChunks * 16) + ((chunk ^ (lane & (kChunks - 1))) << 4),
+                                         __float_as_uint(__uint_as_float(orr[4 * x + 0]) * w_new),
+                                         __float_as_uint(__uint_as_float(orr[4 * x + 1]) * w_new),
+                                         __float_as_uint(__uint_as_float(orr[4 * x + 2]) * w_new),
+                                         __float_as_uint(__uint_as_float(orr[4 * x + 3]) * w_new));
                         }
                     }
+                    __syncwarp();
+#pragma unroll
+                    for (int rr = 0; rr < 32 / kRowsPerInst; ++rr) {
+                        const int rl = rr * kRowsPerInst + lane / kChunks;  // row of the warp this lane serves now
+                        const int ch = lane % kChunks;
+                        float4 val = ld_shared_v4(stage + rl * (kChunks * 16) + ((ch ^ (rl & (kChunks - 1))) << 4));
+                        const float wo = __shfl_sync(0xffffffffu, w_old, rl);
+                        if (row_base + rl < a.sq) {
+                            float4* dst = reinterpret_cast<float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride +
+                                                                    pass * kHalfCols) + ch;
+                            if (a.merge) {
+                                const float4 old = *dst;
+                                val.x = fmaf(old.x, wo, val.x);
+                                val.y = fmaf(old.y, wo, val.y);
+                                val.z = fmaf(old.z, wo, val.z);
+                                val.w = fmaf(old.w, wo, val.w);
+                            }
+                            *dst = val;
+                        }
+                    }
+                    __syncwarp();
                 }
                 if (row_ok) *lse_ptr = lse_new;
             }
         }
     }
 
+    RING_TRACE_LIFE(tid == 0, 4);
     // ---- common exit: every thread arrives here, on success and on a timed-out wait alike ------------
     tcgen05_fence_before_thread_sync();
     __syncthreads();
