@@ -88,3 +88,17 @@ def test_product_never_imports_the_oracle():
                 text = open(os.path.join(dirpath, f)).read()
                 for pat in (r"^\s*(from|import)\s+oracle", r"liboracle", r"oracle[/\\.]oracle", r"attention_oracle"):
                     assert not re.search(pat, text, flags=re.M), f"{f} reaches into the oracle ({pat})"
+
+
+def test_torch_front_end_builds_and_checks_inputs():
+    """The torch extension compiles against this torch, exports its three functions, and its CHECK_INPUT
+    guard rejects a CPU tensor before anything reaches the GPU library."""
+    torch = pytest.importorskip("torch")
+    from ringattention_b200 import build, torch_ops
+    build.build_torch_ext()
+    ext = torch_ops._load()
+    for name in ("block_forward", "ring_forward", "lse_merge_"):
+        assert callable(getattr(ext, name))
+    q = torch.zeros(1, 1, 128, 64, dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+        torch_ops.block_forward(q, q, q)
