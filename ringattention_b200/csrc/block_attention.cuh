@@ -197,6 +197,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         const int nslots = kv == 0 ? T::kKStages : T::kVStages;
                         const int slot = (kv == 0 ? 0 : T::kKStages) + j % nslots;
                         const int use = j / nslots;  // how many times this slot has been filled before
+                        RING_TRACE_STAMP(true, 28 + 2 * kv);
                         if (use > 0) {
                             ok = mbar_wait(bar_kv_empty(slot), (use - 1) & 1, abort_flag, a.status, kDevLoadWaitEmpty);
                             if (!ok) break;
@@ -212,6 +213,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         for (int x = 0; x < kBoxes; ++x)
                             tma_load_4d(smem_kv(slot) + x * kBoxBytes, tm, bar_kv_full(slot), x * 64, j * T::kBlockN, h, b);
 #endif
+                        RING_TRACE_STAMP(true, 29 + 2 * kv);
                         if (j == 0 && kv == 0 && tile1_valid) {
                             mbar_arrive_expect_tx(bar_q_full(1), kTileBytes);
 #pragma unroll

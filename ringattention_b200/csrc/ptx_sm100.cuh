@@ -84,10 +84,19 @@ __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
 // raises the CTA-wide abort flag (shared memory), records `code` in the global status word and
 // returns false; every other wait of the CTA sees the flag within a few hundred polls and
 // returns false as well, so all roles fall through to the common exit, where TMEM is freed.
+#ifndef RING_WAIT_SPIN
+#define RING_WAIT_SPIN 1  // non-blocking tests before the suspending try_wait
+#endif
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s; a legitimate wait is microseconds
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
+    // mbarrier.try_wait costs about 200 clocks even when the phase is already complete (measured), the non-blocking
+    // test_wait a few tens: test first.  A phase that is not complete yet is waited for with try_wait, which suspends
+    // the thread; polling test_wait instead takes issue slots from the softmax warps and was slower.
+#pragma unroll 1
+    for (int i = 0; i < RING_WAIT_SPIN; ++i)
+        if (mbar_test_wait(bar, parity)) return true;
 #pragma unroll 1
     for (int i = 0; i < 128; ++i)
         if (mbar_try_wait(bar, parity)) return true;
