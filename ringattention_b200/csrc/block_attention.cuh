@@ -80,6 +80,11 @@ struct BlockFwdArgs {
 #endif
 
 constexpr float kRescaleThresholdLog2 = 8.0f;
+#ifdef RING_DEBUG_SOFTMAX_ONLY  // timing experiments: softmax warps run without MMAs, loads or waits (results are garbage)
+constexpr bool kSoftmaxOnly = true;
+#else
+constexpr bool kSoftmaxOnly = false;
+#endif
 
 #ifndef RING_PV_AFTER_QK
 #define RING_PV_AFTER_QK 0
@@ -182,7 +187,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         setmaxnreg_dec<T::kProducerRegs>();
         if (warp == T::kLoadWarp) {
             // =================================================================== TMA producer
-            if (lane == 0 && nblk > 0) {
+            if (lane == 0 && nblk > 0 && !kSoftmaxOnly) {
                 mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
 #pragma unroll
                 for (int x = 0; x < kBoxes; ++x)
@@ -228,7 +233,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             // =================================================================== UMMA issuer: S = Q K^T, both tiles
             // (One thread sustains roughly one tcgen05.mma per 110 clocks, so the three MMA streams of the CTA
             //  -- S for both tiles, P V for tile 0, P V for tile 1 -- are issued by three different warps.)
-            if (lane == 0 && nblk > 0) {
+            if (lane == 0 && nblk > 0 && !kSoftmaxOnly) {
                 // S = Q_t K^T into the shared S buffer: D/16 instructions of 128 x 128 x 16
                 auto issue_qk = [&](int t, int kslot) {
 #pragma unroll
@@ -270,7 +275,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         } else if (warp == T::kMmaWarp + 1 || warp == T::kMmaWarp + 2) {
             // =================================================================== UMMA issuer: O_t += P_t V, one warp per tile
             const int t = warp - (T::kMmaWarp + 1);
-            if (lane == 0 && nblk > 0 && t < ntiles) {
+            if (lane == 0 && nblk > 0 && t < ntiles && !kSoftmaxOnly) {
                 // kBlockN/16 instructions of 128 x D x 16, A = 16-bit P in TMEM, B = V MN-major in shared memory
                 bool ok = true;
 #pragma unroll 1
@@ -328,7 +333,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             for (int j = 0; j < nblk; ++j) {
                 uint32_t sr[128];
                 float* s = reinterpret_cast<float*>(sr);
-                ok = mbar_wait(bar_s_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
+                ok = kSoftmaxOnly || mbar_wait(bar_s_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 0);
@@ -395,7 +400,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 
                 // P_t(j - 1) V must be complete before P_t is overwritten or O_t rescaled (it long is)
                 if (j > 0) {
-                    ok = mbar_wait(bar_o_done(t), (j - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
+                    ok = kSoftmaxOnly || mbar_wait(bar_o_done(t), (j - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tcgen05_fence_after_thread_sync();
@@ -434,7 +439,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             RING_TRACE_LIFE(tid == 0, 3);
             // ---- epilogue: O / l, LSE, optional fold into an earlier partial -----------------------
             if (ok && nblk > 0) {
-                ok = mbar_wait(bar_o_done(t), (nblk - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
+                ok = kSoftmaxOnly || mbar_wait(bar_o_done(t), (nblk - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
                 ok = __all_sync(0xffffffffu, ok);
                 if (ok) tcgen05_fence_after_thread_sync();
             }

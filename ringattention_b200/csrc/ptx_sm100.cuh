@@ -89,13 +89,14 @@ __device__ __forceinline__ float4 ld_shared_v4(uint32_t addr) {
 #endif
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s; a legitimate wait is microseconds
 
+template <int kTests = RING_WAIT_SPIN>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
     // mbarrier.try_wait costs about 200 clocks even when the phase is already complete (measured), the non-blocking
     // test_wait a few tens: test first.  A phase that is not complete yet is waited for with try_wait, which suspends
     // the thread; polling test_wait instead takes issue slots from the softmax warps and was slower.
 #pragma unroll 1
-    for (int i = 0; i < RING_WAIT_SPIN; ++i)
+    for (int i = 0; i < kTests; ++i)
         if (mbar_test_wait(bar, parity)) return true;
 #pragma unroll 1
     for (int i = 0; i < 128; ++i)
