@@ -80,6 +80,9 @@ struct BlockFwdArgs {
 #endif
 
 constexpr float kRescaleThresholdLog2 = 8.0f;
+#ifdef RING_DEBUG_LOAD_ONLY  // timing experiments: only the TMA loads run (slots are freed at once; results are garbage)
+#define RING_DEBUG_NO_SOFTMAX 1
+#endif
 #ifdef RING_DEBUG_SOFTMAX_ONLY  // timing experiments: softmax warps run without MMAs, loads or waits (results are garbage)
 constexpr bool kSoftmaxOnly = true;
 #else
@@ -255,14 +258,20 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         RING_TRACE_STAMP(true, 16 + 4 * t);
                         if (j == 0) ok = mbar_wait(bar_q_full(t), 0, abort_flag, a.status, kDevMmaWaitQ);
                         // the buffer is free once its previous content has been read out by the tile it was for
+#ifndef RING_DEBUG_LOAD_ONLY
                         if (ok && (j > 0 || t > 0)) {
                             ok = mbar_wait(bar_s_free, reads & 1, abort_flag, a.status, kDevMmaWaitS);
                             ++reads;
                         }
+#endif
                         RING_TRACE_STAMP(true, 17 + 4 * t);
                         if (ok && t == 0) ok = mbar_wait(bar_kv_full(kslot), kphase, abort_flag, a.status, kDevMmaWaitKV);
                         if (!ok) break;
                         RING_TRACE_STAMP(true, 18 + 4 * t);
+#ifdef RING_DEBUG_LOAD_ONLY
+                        mbar_arrive(bar_kv_empty(kslot));
+                        continue;
+#endif
                         tcgen05_fence_after_thread_sync();
                         issue_qk(t, kslot);
                         umma_commit(bar_s_full(t));
@@ -282,6 +291,12 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 for (int j = 0; j < nblk && ok; ++j) {
                     const int vslot = T::kKStages + j % T::kVStages;
                     const uint32_t vphase = static_cast<uint32_t>((j / T::kVStages) & 1);
+#ifdef RING_DEBUG_LOAD_ONLY
+                    ok = mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV);
+                    if (!ok) break;
+                    mbar_arrive(bar_kv_empty(vslot));
+                    continue;
+#endif
                     ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
                          mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV);
                     if (!ok) break;
@@ -317,7 +332,11 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         setmaxnreg_inc<T::kSoftmaxRegs>();
         const int t = warp >> 2;  // Q tile of this warpgroup
         const int quarter = warp & 3;
+#ifdef RING_DEBUG_NO_SOFTMAX
+        if (false) {
+#else
         if (t < ntiles) {
+#endif
             const int row = r0 + t * 128 + quarter * 32 + lane;  // row of the Q shard == TMEM lane
             const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
             const uint32_t t_s = tmem_base + lane_addr + T::kTmemS;
