@@ -403,16 +403,25 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < 128; i += 4) {
+#if RING_POLY_EVERY > 0
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         const float x = fmaf(s[i + u], c, nms);
-#if RING_POLY_EVERY > 0
                         s[i + u] = ((i + u) % RING_POLY_EVERY == RING_POLY_EVERY - 1) ? ex2_poly(x) : ex2_approx(x);
-#else
-                        s[i + u] = ex2_approx(x);
-#endif
                     }
-                    a0 += s[i]; a1 += s[i + 1]; a2 += s[i + 2]; a3 += s[i + 3];
+#else
+                    // packed fp32 pairs (fma.rn.f32x2 / add.rn.f32x2): same roundings as the scalar forms, half the
+                    // issue slots; the S row sits in consecutive registers, so the pairs cost no moves
+#pragma unroll
+                    for (int u = 0; u < 4; u += 2) {
+                        float x0, x1;
+                        ffma2(x0, x1, s[i + u], s[i + u + 1], c, c, nms, nms);
+                        s[i + u] = ex2_approx(x0);
+                        s[i + u + 1] = ex2_approx(x1);
+                    }
+#endif
+                    fadd2(a0, a1, a0, a1, s[i], s[i + 1]);
+                    fadd2(a2, a3, a2, a3, s[i + 2], s[i + 3]);
                 }
                 l_run = fmaf(l_run, alpha, (a0 + a1) + (a2 + a3));
                 RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 3);
