@@ -33,7 +33,8 @@ typedef enum RingStatus {
     RING_ERR_NCCL = -3,             /* an NCCL call failed or NCCL could not be loaded */
     RING_ERR_DEVICE_TIMEOUT = -4,   /* a bounded wait inside a kernel ran out; the device status word says which */
     RING_ERR_NO_CONTEXT = -5,       /* ring_attention() with npes > 1 before ring_set_default_ctx() */
-    RING_ERR_UNSUPPORTED = -6
+    RING_ERR_UNSUPPORTED = -6,
+    RING_ERR_HOST_TIMEOUT = -7      /* ring_ctx_synchronize_timeout: the deadline passed with work still pending */
 } RingStatus;
 
 #define RING_UNIQUE_ID_BYTES 128
@@ -146,6 +147,15 @@ int ring_step_plan(int world, int rank, int step, int causal, int causal_skip_ex
 /* Blocks until everything the context has enqueued is done and returns the device status
  * (RING_OK or RING_ERR_DEVICE_TIMEOUT / RING_ERR_CUDA). */
 int ring_ctx_synchronize(RingCtx* ctx);
+
+/*
+ * The same with a deadline, for failure detection on the host: polls the completion of the last forward, the
+ * exchange stream and the copy-out stream without blocking on the device, and returns RING_ERR_HOST_TIMEOUT if
+ * they are not all done after timeout_ms (a peer that stopped, a stream blocked upstream).  The context is left
+ * untouched; calling again waits further.  timeout_ms < 0 waits without limit.  No counterpart in the reference,
+ * which ends every call in cudaDeviceSynchronize (csrc/ring_attention.cu:721) and so hangs with its peer.
+ */
+int ring_ctx_synchronize_timeout(RingCtx* ctx, int timeout_ms);
 
 /*
  * Per-step timings of the last ring_attention_fwd() (needs RING_OPT_RECORD_TIMINGS = 1 and a prior

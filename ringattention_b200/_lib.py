@@ -17,6 +17,7 @@ RING_ERR_NCCL = -3
 RING_ERR_DEVICE_TIMEOUT = -4
 RING_ERR_NO_CONTEXT = -5
 RING_ERR_UNSUPPORTED = -6
+RING_ERR_HOST_TIMEOUT = -7
 RING_UNIQUE_ID_BYTES = 128
 RING_MERGE_SEPARATE_KERNEL = 0
 RING_MERGE_FUSED_EPILOGUE = 1
@@ -64,6 +65,7 @@ SYMBOLS = {
     "ring_attention_fwd": (c_int, [c_void_p, ctypes.POINTER(Ring_fwd_params)]),
     "ring_attention_fwd_host": (c_int, [c_void_p, ctypes.POINTER(Ring_fwd_params), c_int]),
     "ring_ctx_synchronize": (c_int, [c_void_p]),
+    "ring_ctx_synchronize_timeout": (c_int, [c_void_p, c_int]),
     "ring_step_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(RingStepPlan)]),
     "ring_ctx_get_timings": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_float), ctypes.POINTER(c_float), c_int]),
     "ring_attention_block_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,

@@ -210,8 +210,13 @@ class RingContext:
         p.is_bf16 = int(q.dtype == torch.bfloat16)
         check(_lib.load().ring_attention_fwd_host(self._h, ctypes.byref(p), int(chunks)), "ring_attention_fwd_host")
 
-    def synchronize(self) -> None:
-        check(_lib.load().ring_ctx_synchronize(self._h), "ring_ctx_synchronize")
+    def synchronize(self, timeout_ms: Optional[int] = None) -> None:
+        """Waits for everything the context enqueued.  With timeout_ms the wait is polled from the host and raises
+        RingError (code RING_ERR_HOST_TIMEOUT) when the deadline passes; the context stays usable."""
+        if timeout_ms is None:
+            check(_lib.load().ring_ctx_synchronize(self._h), "ring_ctx_synchronize")
+        else:
+            check(_lib.load().ring_ctx_synchronize_timeout(self._h, int(timeout_ms)), "ring_ctx_synchronize_timeout")
 
     def timings(self):
         """(compute_ms, comm_ms, exposed_ms) lists of the last forward, one entry per ring step."""

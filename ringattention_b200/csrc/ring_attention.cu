@@ -12,6 +12,7 @@
 // stream into two alternating receive buffers instead of an in-kernel NVSHMEM get into a single buffer
 // (:611-619); errors are returned, not printed-and-exit (csrc/utils.h:1-11).
 #include <atomic>
+#include <chrono>
 #include <cmath>
 #include <cstdarg>
 #include <cstdio>
@@ -20,6 +21,7 @@
 #include <dlfcn.h>
 #include <mutex>
 #include <string>
+#include <thread>
 #include <vector>
 
 #include <cuda.h>
@@ -1164,6 +1166,43 @@ int ring_ctx_synchronize(RingCtx* ctx) {
     int status = 0;
     int rc = read_status(&status);
     if (rc) return rc;
+    if (ctx->comm) {
+        ncclResult_t async = ncclSuccess;
+        RING_NCCL(nccl().CommGetAsyncError(ctx->comm, &async));
+        if (async != ncclSuccess) return fail(RING_ERR_NCCL, "NCCL async error: %s", nccl().GetErrorString(async));
+    }
+    if (status != 0) return fail(RING_ERR_DEVICE_TIMEOUT, "a bounded wait inside a kernel ran out (device status %d)", status);
+    return RING_OK;
+}
+
+// Host-side failure detection: the same as ring_ctx_synchronize, but gives up after `timeout_ms`.  A forward
+// whose peer stopped (its exchange stream then waits for a flag or an NCCL message that never comes), or whose
+// stream is blocked upstream, never completes; this call notices without touching the device: it polls the
+// completion event of the last forward and the exchange stream, and returns RING_ERR_HOST_TIMEOUT when the
+// deadline passes.  The context is left as it is: the caller decides (wait longer, or tear the job down).
+int ring_ctx_synchronize_timeout(RingCtx* ctx, int timeout_ms) {
+    if (!ctx) return fail(RING_ERR_INVALID_ARGUMENT, "null context");
+    if (timeout_ms < 0) return ring_ctx_synchronize(ctx);
+    const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+    for (;;) {
+        cudaError_t e1 = ctx->have_call_done ? cudaEventQuery(ctx->ev_call_done) : cudaSuccess;
+        cudaError_t e2 = ctx->comm_stream ? cudaStreamQuery(ctx->comm_stream) : cudaSuccess;
+        cudaError_t e3 = ctx->d2h_stream ? cudaStreamQuery(ctx->d2h_stream) : cudaSuccess;
+        if (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) break;
+        for (cudaError_t e : {e1, e2, e3})
+            if (e != cudaSuccess && e != cudaErrorNotReady) RING_CUDA(e);
+        if (std::chrono::steady_clock::now() >= deadline)
+            return fail(RING_ERR_HOST_TIMEOUT, "the forward did not finish within %d ms (%s%s%s still pending)", timeout_ms,
+                        e1 != cudaSuccess ? "compute " : "", e2 != cudaSuccess ? "exchange " : "", e3 != cudaSuccess ? "copy-out " : "");
+        std::this_thread::sleep_for(std::chrono::microseconds(200));
+    }
+    // everything this context enqueued is done: read the status word without a device-wide synchronisation
+    DeviceState* st = nullptr;
+    int rc = device_state(&st);
+    if (rc) return rc;
+    int status = 0;
+    RING_CUDA(cudaMemcpyAsync(&status, st->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->comm_stream));
+    RING_CUDA(cudaStreamSynchronize(ctx->comm_stream));
     if (ctx->comm) {
         ncclResult_t async = ncclSuccess;
         RING_NCCL(nccl().CommGetAsyncError(ctx->comm, &async));

@@ -42,3 +42,50 @@ def test_recorded_failure_stops_later_kernels_until_reset():
     ctx.synchronize()
     assert not torch.isnan(out).any() and ra.device_status() == 0
     ctx.destroy()
+
+
+def test_host_deadline_notices_a_forward_that_does_not_finish():
+    """A forward queued behind a stream wait that nothing satisfies yet (what a stopped peer looks like from this
+    rank's side: a stream waiting for a flag): synchronize(timeout_ms) gives up on time and says so, nothing on the
+    device is disturbed, and once the flag is written the same forward completes with correct results."""
+    import time
+
+    import torch
+    import ringattention_b200 as ra
+    from cuda.bindings import driver
+    from oracle import oracle
+
+    B, H, S, D = 1, 2, 256, 64
+    qh, kh, vh = synthetic.make_qkv(21, B, H, D, 0, S)
+    q, k, v = (to_dev(x) for x in (qh, kh, vh))
+    out = torch.zeros((B, H, S, D), device="cuda")
+    lse = torch.zeros((B, H, S), device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ra.device_status_reset()
+    ctx = ra.RingContext.create(0, 1, None)
+    work, side = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    released = False
+    try:
+        (err,) = driver.cuStreamWaitValue32(work.cuda_stream, flag.data_ptr(), 1, driver.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+        assert int(err) == 0
+        ctx.forward(q, k, v, out, lse, stream=work.cuda_stream)
+        t0 = time.perf_counter()
+        with pytest.raises(ra.RingError) as e:
+            ctx.synchronize(timeout_ms=300)
+        waited = time.perf_counter() - t0
+        assert e.value.code == ra.RING_ERR_HOST_TIMEOUT and "compute" in str(e.value)
+        assert 0.25 <= waited <= 2.0
+        with torch.cuda.stream(side):
+            flag.fill_(1)
+        released = True
+        ctx.synchronize(timeout_ms=10000)   # now it finishes
+    finally:
+        if not released:
+            with torch.cuda.stream(side):
+                flag.fill_(1)
+        torch.cuda.synchronize()
+    want_o, want_lse = oracle.attention_fwd(qh, kh, vh, D ** -0.5)
+    assert np.abs(out.cpu().numpy() - want_o).max() <= 2e-3
+    assert np.abs(lse.cpu().numpy() - want_lse).max() <= 1e-4
+    ctx.destroy()
