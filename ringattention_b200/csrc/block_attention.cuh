@@ -504,6 +504,19 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 float* o_base = a.o + b * a.o_batch_stride + h * a.o_head_stride;
 #pragma unroll 1
                 for (int pass = 0; pass < 2; ++pass) {
+                    // when folding into an earlier partial, fetch its values first: all loads of the pass are in
+                    // flight together and their latency passes under the TMEM read-out and the staging
+                    float4 old[32 / kRowsPerInst];
+                    if (a.merge) {
+#pragma unroll
+                        for (int rr = 0; rr < 32 / kRowsPerInst; ++rr) {
+                            const int rl = rr * kRowsPerInst + lane / kChunks;
+                            old[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (row_base + rl < a.sq)
+                                old[rr] = *(reinterpret_cast<const float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride +
+                                                                            pass * kHalfCols) + lane % kChunks);
+                        }
+                    }
 #pragma unroll
                     for (int i = 0; i < kHalfCols / 32; ++i) {
                         uint32_t orr[32];
@@ -531,18 +544,15 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         const int ch = lane % kChunks;
                         float4 val = ld_shared_v4(stage + rl * (kChunks * 16) + ((ch ^ (rl & (kChunks - 1))) << 4));
                         const float wo = __shfl_sync(0xffffffffu, w_old, rl);
-                        if (row_base + rl < a.sq) {
-                            float4* dst = reinterpret_cast<float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride +
-                                                                    pass * kHalfCols) + ch;
-                            if (a.merge) {
-                                const float4 old = *dst;
-                                val.x = fmaf(old.x, wo, val.x);
-                                val.y = fmaf(old.y, wo, val.y);
-                                val.z = fmaf(old.z, wo, val.z);
-                                val.w = fmaf(old.w, wo, val.w);
-                            }
-                            *dst = val;
+                        if (a.merge) {
+                            val.x = fmaf(old[rr].x, wo, val.x);
+                            val.y = fmaf(old[rr].y, wo, val.y);
+                            val.z = fmaf(old[rr].z, wo, val.z);
+                            val.w = fmaf(old[rr].w, wo, val.w);
                         }
+                        if (row_base + rl < a.sq)
+                            *(reinterpret_cast<float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride +
+                                                        pass * kHalfCols) + ch) = val;
                     }
                     __syncwarp();
                 }
