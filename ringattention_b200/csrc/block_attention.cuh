@@ -65,6 +65,7 @@ struct BlockFwdArgs {
     int causal;       // key j of the shard is visible to query i of the shard iff j <= i + diag
     int diag;         // (global index of Q row 0) - (global index of K row 0)
     int merge;        // 0: overwrite o/lse; 1: o/lse already hold a partial of the same rows, fold into it
+    int rows_per_cta; // 256 (two Q tiles per CTA) or 128 (one tile: twice the CTAs, for grids that would leave SMs idle)
     int* status;      // device status word
 #ifdef RING_TRACE
     long long* trace;  // debug builds only: clock64 stamps of CTA (0,0), 32 slots per K/V block
@@ -135,8 +136,8 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     RING_TRACE_LIFE(tid == 0, 0);
 
     // Under a causal mask the CTAs of the last Q rows have the most K/V blocks to visit: launch them first.
-    const int r0 = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * T::kBlockM;  // first Q row of this CTA
-    const bool tile1_valid = (r0 + 128) < a.sq;
+    const int r0 = (a.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x) * a.rows_per_cta;  // first Q row of this CTA
+    const bool tile1_valid = a.rows_per_cta > 128 && (r0 + 128) < a.sq;
     const int ntiles = tile1_valid ? 2 : 1;
 
     if (tid == 0) {
@@ -179,7 +180,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
     const int h = bh - b * a.heads;
     int nblk = (a.sk + T::kBlockN - 1) / T::kBlockN;  // K/V blocks to visit
     if (a.causal) {
-        const int last_row = min(r0 + T::kBlockM, a.sq) - 1;
+        const int last_row = min(r0 + a.rows_per_cta, a.sq) - 1;
         const int last_key = last_row + a.diag;       // last visible key index of the CTA's rows
         const int vis_blk = last_key < 0 ? 0 : last_key / T::kBlockN + 1;
         nblk = min(nblk, vis_blk);

@@ -124,6 +124,7 @@ NcclApi& nccl() {
 // ------------------------------------------------------------------------------------------ per-device state
 struct DeviceState {
     int* d_status = nullptr;  // device status word written by kernels whose bounded waits ran out
+    int sm_count = 0;
     bool attr_set[2][2] = {{false, false}, {false, false}};  // [dim==128][bf16]
 };
 
@@ -139,6 +140,7 @@ int device_state(DeviceState** out) {
     if (!st.d_status) {
         RING_CUDA(cudaMalloc(&st.d_status, sizeof(int)));
         RING_CUDA(cudaMemset(st.d_status, 0, sizeof(int)));
+        RING_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
     }
     *out = &st;
     return RING_OK;
@@ -276,7 +278,11 @@ int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t st
     a.trace = g_trace;
 #endif
 
-    dim3 grid((L.sq + Traits::kBlockM - 1) / Traits::kBlockM, L.batch * L.heads);
+    // Two Q tiles per CTA keep the tensor pipe busiest, but a grid that covers at most half of the SMs that way
+    // (one head of a short shard, as in the reference's own driver) finishes sooner with one tile per CTA.
+    a.rows_per_cta = Traits::kBlockM;
+    if (L.sq > 128 && ((L.sq + Traits::kBlockM - 1) / Traits::kBlockM) * L.batch * L.heads * 2 <= st->sm_count) a.rows_per_cta = 128;
+    dim3 grid((L.sq + a.rows_per_cta - 1) / a.rows_per_cta, L.batch * L.heads);
     dim3 block(Traits::kNThreads);
     kernel<<<grid, block, Traits::kSmemSize, stream>>>(tq, tk, tv, a);
     RING_CUDA(cudaGetLastError());
@@ -1383,6 +1389,7 @@ int launch_block_static(const StaticChunk& c, StaticSetup* s, cudaStream_t strea
 #ifdef RING_TRACE
     a.trace = nullptr;
 #endif
+    a.rows_per_cta = Traits::kBlockM;
     dim3 grid((c.sq + Traits::kBlockM - 1) / Traits::kBlockM, c.batch * c.heads);
     kernel<<<grid, dim3(Traits::kNThreads), Traits::kSmemSize, stream>>>(tq, tk, tv, a);
     RING_CUDA(cudaGetLastError());
