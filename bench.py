@@ -34,7 +34,7 @@ UNIT = "TFLOP/s"
 
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE block-kernel launch at the bench shape, from the ncu
 # capture summarised in profiles/ (None until a capture exists).
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 301.9e6  # 201.4 MB read + 97.5 MB written (profiles/block_attention_b2_h16_s8192_d128.md)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 301.9e6  # 201.7 MB read + 100.2 MB written (profiles/block_attention_b2_h16_s8192_d128.md)
 
 
 def flops_per_rank(world: int) -> float:
