@@ -280,8 +280,13 @@ int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t st
 
     // Two Q tiles per CTA keep the tensor pipe busiest, but a grid that covers at most half of the SMs that way
     // (one head of a short shard, as in the reference's own driver) finishes sooner with one tile per CTA.
+    // (RING_ROWS_PER_CTA = 128 or 256 in the environment overrides the choice; the tests use it to run both forms.)
     a.rows_per_cta = Traits::kBlockM;
     if (L.sq > 128 && ((L.sq + Traits::kBlockM - 1) / Traits::kBlockM) * L.batch * L.heads * 2 <= st->sm_count) a.rows_per_cta = 128;
+    if (const char* e = std::getenv("RING_ROWS_PER_CTA")) {
+        const int forced = std::atoi(e);
+        if (forced == 128 || forced == Traits::kBlockM) a.rows_per_cta = forced;
+    }
     dim3 grid((L.sq + a.rows_per_cta - 1) / a.rows_per_cta, L.batch * L.heads);
     dim3 block(Traits::kNThreads);
     kernel<<<grid, block, Traits::kSmemSize, stream>>>(tq, tk, tv, a);

@@ -12,6 +12,15 @@ from tests.gpu_util import assert_parity, to_dev
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True, params=["auto", "256", "128"])
+def rows_per_cta(request, monkeypatch):
+    """Every test runs with the launcher's own choice of Q rows per CTA and with each form forced."""
+    if request.param == "auto":
+        monkeypatch.delenv("RING_ROWS_PER_CTA", raising=False)
+    else:
+        monkeypatch.setenv("RING_ROWS_PER_CTA", request.param)
+
 GOLDEN = sorted(glob.glob(os.path.join(os.path.dirname(__file__), "golden", "*.npz")))
 
 
