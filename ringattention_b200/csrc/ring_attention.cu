@@ -1200,6 +1200,7 @@ int ring_ctx_synchronize_timeout(RingCtx* ctx, int timeout_ms) {
         cudaError_t e2 = ctx->comm_stream ? cudaStreamQuery(ctx->comm_stream) : cudaSuccess;
         cudaError_t e3 = ctx->d2h_stream ? cudaStreamQuery(ctx->d2h_stream) : cudaSuccess;
         if (e1 == cudaSuccess && e2 == cudaSuccess && e3 == cudaSuccess) break;
+        (void)cudaGetLastError();  // "not ready" is recorded as the thread's last error; a later launch check must not see it
         for (cudaError_t e : {e1, e2, e3})
             if (e != cudaSuccess && e != cudaErrorNotReady) RING_CUDA(e);
         if (std::chrono::steady_clock::now() >= deadline)
