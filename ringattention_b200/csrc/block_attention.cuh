@@ -8,15 +8,18 @@
 // the standalone merge kernel.
 //
 // Mapping to the hardware
-//   * a CTA owns two 128-row Q tiles of one (batch, head) and walks the K/V shard in 128-row blocks;
-//   * one thread issues TMA loads (Q once, then K_j, V_j through a ring of kStages shared-memory
-//     slots, 128-byte swizzle, 64-element boxes);
-//   * one thread issues tcgen05.mma.  S_t = Q_t K_j^T (both operands K-major in shared memory, N = 128:
-//     a narrower N would re-read Q from shared memory, whose ~75 B/clock operand bandwidth is what bounds
-//     these instructions) goes to ONE S buffer of 128 TMEM columns that the two Q tiles use in turn;
-//     O_t += P_t V_j reads P_t from its own 64 TMEM columns (16-bit pairs) and V_j MN-major from shared
-//     memory, so V is never transposed (the reference needs ldmatrix.trans, csrc/kernel_traits.h:39,93-103)
-//     and the PV product spends no shared-memory bandwidth on its A operand;
+//   * a CTA owns two 128-row Q tiles of one (batch, head) and walks the K/V shard in 128-row blocks (one
+//     tile per CTA when the two-tile grid would leave more than half of the SMs idle, args.rows_per_cta);
+//   * one thread issues TMA loads (Q once, then K_j and V_j through two rings of shared-memory slots,
+//     128-byte swizzle, 64-element boxes);
+//   * three threads of three warps issue tcgen05.mma, because one thread sustains only about one 128x128x16
+//     instruction per 100 clocks while the pipe takes one per ~70.  The first issues S_t = Q_t K_j^T for both
+//     tiles (both operands K-major in shared memory, N = 128: a narrower N would re-read Q from shared memory,
+//     whose ~75 B/clock operand bandwidth is what bounds these instructions) into ONE S buffer of 128 TMEM
+//     columns that the two Q tiles use in turn; the other two issue O_t += P_t V_j for tile 0 / 1, reading P_t
+//     from its own 64 TMEM columns (16-bit pairs) and V_j MN-major from shared memory, so V is never transposed
+//     (the reference needs ldmatrix.trans, csrc/kernel_traits.h:39,93-103) and the PV product spends no
+//     shared-memory bandwidth on its A operand;
 //   * two softmax warpgroups (one per Q tile, one thread per row = one TMEM lane).  A warpgroup reads its
 //     S_t(j) into registers and hands the S buffer to the other tile at once; because P has columns of its
 //     own, S_t(j+1) is computed while the OTHER tile runs its softmax, and the serial chain per tile is
@@ -25,7 +28,9 @@
 //     registers; a new maximum is adopted only when it exceeds the one in use by more than 2^8 (the stale
 //     maximum is exact algebra: it cancels in O / l and in the LSE), and then O is rescaled in TMEM;
 //   * the producer warpgroup gives registers back (setmaxnreg) and the softmax warpgroups take them, so a
-//     whole S row plus its packed probabilities stay in registers without spilling.
+//     whole S row plus its packed probabilities stay in registers without spilling;
+//   * the epilogue stages O through the Q tile's shared memory so that global stores (and, when folding into
+//     an earlier partial, loads) cover whole row pieces.
 // Every mbarrier wait is bounded (ptx::mbar_wait); on expiry the CTA records a status code, all roles
 // fall through to the common exit and TMEM is released.
 #pragma once
