@@ -54,7 +54,6 @@ enum DeviceStatus : int {
     kDevMmaWaitS = 114,
     kDevSoftmaxWaitS = 121,
     kDevSoftmaxWaitO = 122,
-    kDevSoftmaxWaitTurn = 123,
 };
 
 struct BlockFwdArgs {
@@ -95,9 +94,6 @@ constexpr bool kSoftmaxOnly = true;
 constexpr bool kSoftmaxOnly = false;
 #endif
 
-#ifndef RING_PV_AFTER_QK
-#define RING_PV_AFTER_QK 0
-#endif
 #ifndef RING_POLY_EVERY
 #define RING_POLY_EVERY 0  // N > 0: every N-th exponential is evaluated on the FMA pipe instead of the MUFU
 #endif
@@ -216,17 +212,11 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                             ok = mbar_wait(bar_kv_empty(slot), (use - 1) & 1, abort_flag, a.status, kDevLoadWaitEmpty);
                             if (!ok) break;
                         }
-#ifdef RING_DEBUG_HALF_LOAD
-                        mbar_arrive_expect_tx(bar_kv_full(slot), kBoxBytes);
-                        const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
-                        tma_load_4d(smem_kv(slot), tm, bar_kv_full(slot), 0, j * T::kBlockN, h, b);
-#else
                         mbar_arrive_expect_tx(bar_kv_full(slot), kTileBytes);
                         const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
 #pragma unroll
                         for (int x = 0; x < kBoxes; ++x)
                             tma_load_4d(smem_kv(slot) + x * kBoxBytes, tm, bar_kv_full(slot), x * 64, j * T::kBlockN, h, b);
-#endif
                         RING_TRACE_STAMP(true, 29 + 2 * kv);
                         if (j == 0 && kv == 0 && tile1_valid) {
                             mbar_arrive_expect_tx(bar_q_full(1), kTileBytes);
@@ -306,18 +296,6 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                     ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
                          mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV);
                     if (!ok) break;
-#if RING_PV_AFTER_QK
-                    // Tile t has just finished block j and is reading its S(j + 1): that read-out releases the S
-                    // buffer for the OTHER tile's next S, which the other tile will soon be waiting for, while this
-                    // PV product has a whole softmax of slack.  Let that S go through the tensor pipe first.
-                    if (ntiles == 2) {
-                        const int jn = t == 0 ? j + 1 : j + 2;  // block whose S the other tile gets now
-                        if (jn < nblk) {
-                            ok = mbar_wait(bar_s_full(t ^ 1), jn & 1, abort_flag, a.status, kDevMmaWaitS);
-                            if (!ok) break;
-                        }
-                    }
-#endif
                     RING_TRACE_STAMP(true, 24 + 2 * t);
                     tcgen05_fence_after_thread_sync();
 #pragma unroll

@@ -333,13 +333,6 @@ __device__ __forceinline__ float ex2_poly(float x) {
     p = fmaf(p, f, 9.999992847e-01f);
     return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
-// Same instruction, but pinned between the surrounding volatile statements (barrier waits / arrivals):
-// used where the exponentials must stay inside a window in which this warp owns the MUFU.
-__device__ __forceinline__ float ex2_approx_pinned(float x) {
-    float y;
-    asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
