@@ -210,16 +210,19 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         # the public host-buffer call: pinned Q, K, V in, pinned O, LSE out, copies inside the timed region
         ctx.forward_host(hq, hk, hv, h_out, h_lse, chunks=args.e2e_chunks, softmax_scale=scale)
 
+    per_step = {}  # name of the timed function -> this rank's per-step milliseconds of its last timed run
+
     def timed(fn, steps):
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
+        marks = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+        marks[0].record(stream)
+        for i in range(steps):
             fn()
-        e1.record(stream)
-        e1.synchronize()
+            marks[i + 1].record(stream)
+        marks[-1].synchronize()
         barrier()
-        ms = e0.elapsed_time(e1)
+        ms = marks[0].elapsed_time(marks[-1])
+        per_step[fn.__name__] = [marks[i].elapsed_time(marks[i + 1]) for i in range(steps)]
         if dist is not None:
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -243,6 +246,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         sampler.start()
     launches0 = ra.kernel_launch_count()
     total_ms = timed(step_resident, args.steps)
+    steps_ms = list(per_step["step_resident"])
     launches = ra.kernel_launch_count() - launches0
     ctx.synchronize()  # also checks the device status word
     compute_ms, comm_ms, exposed_ms = ctx.timings()  # of the last timed step
@@ -295,7 +299,8 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         step_ms = sum(compute_ms) + sum(exposed_ms)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "ms_per_step_median_rank0": statistics.median(steps_ms),
+            "ms_per_step_min_rank0": min(steps_ms), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f16 (fp32 accumulate)", "data": "synthetic",
             "config": {"workload": workload_name(world), "batch": B, "heads": H, "seq_local": S_LOCAL, "head_dim": D,
                        "causal": False, "parallelism": f"ring{world} (sequence sharded, double-buffered K/V exchange on a side stream)",
