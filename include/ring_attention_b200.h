@@ -28,7 +28,7 @@ extern "C" {
 
 typedef enum RingStatus {
     RING_OK = 0,
-    RING_ERR_INVALID_ARGUMENT = -1, /* null pointer, dim not in {64,128}, seqlen % 128 != 0, uneven shards ... */
+    RING_ERR_INVALID_ARGUMENT = -1, /* null pointer, dim not in {64,128}, non-positive length or scale, misaligned base ... */
     RING_ERR_CUDA = -2,             /* a CUDA runtime/driver call failed; see ring_last_error_string() */
     RING_ERR_NCCL = -3,             /* an NCCL call failed or NCCL could not be loaded */
     RING_ERR_DEVICE_TIMEOUT = -4,   /* a bounded wait inside a kernel ran out; the device status word says which */
@@ -167,6 +167,26 @@ int ring_ctx_synchronize_timeout(RingCtx* ctx, int timeout_ms);
 int ring_ctx_get_timings(RingCtx* ctx, float* compute_ms, float* comm_ms, float* exposed_ms, int n);
 
 /*
+ * The exchange of step i in two parts (same preconditions as ring_ctx_get_timings): wait_ms[i], the time the
+ * exchange stream waited for its go-ahead (peer-copy transport: the destination's "buffer free" flag; NCCL
+ * transport: the compute step that last read the receive buffer), and copy_ms[i], the transfer itself (peer-copy
+ * transport: this rank's push of its own shard).  Bytes moved per step / copy_ms is the achieved link rate.
+ * No counterpart in the reference (its NVSHMEM get is inside the kernel, csrc/ring_attention.cu:611-619).
+ */
+int ring_ctx_get_exchange_timings(RingCtx* ctx, float* wait_ms, float* copy_ms, int n);
+
+/*
+ * Tear-down after a detected failure (ring_ctx_synchronize_timeout returned RING_ERR_HOST_TIMEOUT because a peer
+ * stopped): releases, from the host, every stream wait this context has queued on its own flag block, aborts the
+ * NCCL communicator (ncclCommAbort) and marks the context dead.  Later forwards on it return RING_ERR_UNSUPPORTED;
+ * ring_ctx_destroy() then frees it without a device-wide synchronisation.  Outputs of the aborted forward are
+ * undefined.  Peers that are still alive must keep their contexts (their receive buffers) until this rank has
+ * destroyed its own: the released copies still land there.  No counterpart in the reference, which hangs with its
+ * peer (every call ends in cudaDeviceSynchronize, csrc/ring_attention.cu:721).
+ */
+int ring_ctx_abort(RingCtx* ctx);
+
+/*
  * Replaces: one pass of the flash inner loop of ring_attention_kernel over ONE source shard
  * (csrc/ring_attention.cu:536-609) plus the final normalisation (:621-664).
  * q [B,H,Sq,D], k/v [B,H,Sk,D] -> o [B,H,Sq,D] fp32, lse [B,H,Sq] fp32.  q_off / k_off are the global
@@ -210,7 +230,8 @@ int ring_lse_merge(float* o_acc, float* lse_acc, const float* o_part, const floa
  * the status word it needs at zero itself, but two calls whose kernels overlap on the GPU (different
  * streams, no ordering between them) race on the partials and give wrong results.  Serialise them.
  * A bounded wait that runs out inside a kernel of this path is recorded in the array's own status word,
- * not in the word ring_device_status() reads.
+ * not in the word ring_device_status() reads; ring_static_status() reads it.  When it is non-zero the
+ * outputs of that call are not valid.
  * Asynchronous on `stream` (cudaStream_t as void*).
  */
 #define RING_STATIC_MAX_ROWS 65536
@@ -218,6 +239,13 @@ int ring_lse_merge(float* o_acc, float* lse_acc, const float* o_part, const floa
 int ring_attention_chunked_fwd_static(const void* q, const void* k, const void* v, float* o, float* lse,
                                       int batch, int heads, int sq, int sk, int dim, float softmax_scale,
                                       int causal, int kv_chunk, int is_bf16, void* stream);
+
+/*
+ * No counterpart in the reference.  Status word of the no-allocation path on the current device: waits for
+ * `stream` (the one the call above was given), then stores in *status_out 0 or the code (1xx) of the bounded
+ * wait that ran out inside the last ring_attention_chunked_fwd_static().  Allocates nothing either.
+ */
+int ring_static_status(int* status_out, void* stream);
 
 /* Device status word of the current device: 0, or the code of the bounded wait that ran out
  * (1xx, see csrc/block_attention.cuh).  ring_device_status synchronises the device. */

@@ -68,6 +68,9 @@ SYMBOLS = {
     "ring_ctx_synchronize_timeout": (c_int, [c_void_p, c_int]),
     "ring_step_plan": (c_int, [c_int, c_int, c_int, c_int, c_int, ctypes.POINTER(RingStepPlan)]),
     "ring_ctx_get_timings": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_float), ctypes.POINTER(c_float), c_int]),
+    "ring_ctx_get_exchange_timings": (c_int, [c_void_p, ctypes.POINTER(c_float), ctypes.POINTER(c_float), c_int]),
+    "ring_ctx_abort": (c_int, [c_void_p]),
+    "ring_static_status": (c_int, [ctypes.POINTER(c_int), c_void_p]),
     "ring_attention_block_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                          c_float, c_int, c_int64, c_int64, c_int, c_int, c_void_p]),
     "ring_lse_merge": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),

@@ -22,7 +22,7 @@ from ._lib import Ring_fwd_params, check
 __all__ = [
     "ring_attention", "ring_attention_scaled", "set_params_fprop", "Ring_fwd_params", "RingContext",
     "attention_block_fwd", "lse_merge", "device_status", "device_status_reset", "kernel_launch_count",
-    "attention_chunked_fwd_static",
+    "attention_chunked_fwd_static", "static_status",
 ]
 
 
@@ -225,6 +225,19 @@ class RingContext:
         check(_lib.load().ring_ctx_get_timings(self._h, a, b, c, n), "ring_ctx_get_timings")
         return list(a), list(b), list(c)
 
+    def exchange_timings(self):
+        """(wait_ms, copy_ms) lists of the last forward's exchanges, one entry per ring step: time spent waiting
+        for the go-ahead, and the transfer itself."""
+        n = self.world
+        a, b = ((ctypes.c_float * n)() for _ in range(2))
+        check(_lib.load().ring_ctx_get_exchange_timings(self._h, a, b, n), "ring_ctx_get_exchange_timings")
+        return list(a), list(b)
+
+    def abort(self) -> None:
+        """After synchronize(timeout_ms=...) raised RING_ERR_HOST_TIMEOUT: release every queued wait of this context
+        from the host, abort its communicator and mark it dead; destroy() then returns without waiting for the device."""
+        check(_lib.load().ring_ctx_abort(self._h), "ring_ctx_abort")
+
     def destroy(self) -> None:
         if self._h:
             _lib.load().ring_ctx_destroy(self._h)
@@ -302,3 +315,11 @@ def attention_chunked_fwd_static(q, k, v, o, lse, kv_chunk: int, *, softmax_scal
         _ptr(o, "o", (torch.float32,)), _ptr(lse, "lse", (torch.float32,)), B, H, Sq, Sk, D, scale,
         int(bool(causal)), int(kv_chunk), int(q.dtype == torch.bfloat16), _stream_handle(stream)),
         "ring_attention_chunked_fwd_static")
+
+
+def static_status(stream=None) -> int:
+    """Status word of the no-allocation path: waits for `stream`, then returns 0 or the code of the bounded wait that
+    ran out inside the last attention_chunked_fwd_static() on this device (its outputs are then invalid)."""
+    s = ctypes.c_int(0)
+    check(_lib.load().ring_static_status(ctypes.byref(s), _stream_handle(stream)), "ring_static_status")
+    return s.value

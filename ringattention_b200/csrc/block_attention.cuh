@@ -85,19 +85,6 @@ struct BlockFwdArgs {
 #endif
 
 constexpr float kRescaleThresholdLog2 = 8.0f;
-#ifdef RING_DEBUG_LOAD_ONLY  // timing experiments: only the TMA loads run (slots are freed at once; results are garbage)
-#define RING_DEBUG_NO_SOFTMAX 1
-#endif
-#ifdef RING_DEBUG_SOFTMAX_ONLY  // timing experiments: softmax warps run without MMAs, loads or waits (results are garbage)
-constexpr bool kSoftmaxOnly = true;
-#else
-constexpr bool kSoftmaxOnly = false;
-#endif
-
-#ifndef RING_POLY_EVERY
-#define RING_POLY_EVERY 0  // N > 0: every N-th exponential is evaluated on the FMA pipe instead of the MUFU
-#endif
-
 template <class T>
 __global__ void __launch_bounds__(T::kNThreads, 1)
 ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -192,7 +179,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         setmaxnreg_dec<T::kProducerRegs>();
         if (warp == T::kLoadWarp) {
             // =================================================================== TMA producer
-            if (lane == 0 && nblk > 0 && !kSoftmaxOnly) {
+            if (lane == 0 && nblk > 0) {
                 mbar_arrive_expect_tx(bar_q_full(0), kTileBytes);
 #pragma unroll
                 for (int x = 0; x < kBoxes; ++x)
@@ -232,7 +219,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             // =================================================================== UMMA issuer: S = Q K^T, both tiles
             // (One thread sustains roughly one tcgen05.mma per 110 clocks, so the three MMA streams of the CTA
             //  -- S for both tiles, P V for tile 0, P V for tile 1 -- are issued by three different warps.)
-            if (lane == 0 && nblk > 0 && !kSoftmaxOnly) {
+            if (lane == 0 && nblk > 0) {
                 // S = Q_t K^T into the shared S buffer: D/16 instructions of 128 x 128 x 16
                 auto issue_qk = [&](int t, int kslot) {
 #pragma unroll
@@ -254,20 +241,14 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         RING_TRACE_STAMP(true, 16 + 4 * t);
                         if (j == 0) ok = mbar_wait(bar_q_full(t), 0, abort_flag, a.status, kDevMmaWaitQ);
                         // the buffer is free once its previous content has been read out by the tile it was for
-#ifndef RING_DEBUG_LOAD_ONLY
                         if (ok && (j > 0 || t > 0)) {
                             ok = mbar_wait(bar_s_free, reads & 1, abort_flag, a.status, kDevMmaWaitS);
                             ++reads;
                         }
-#endif
                         RING_TRACE_STAMP(true, 17 + 4 * t);
                         if (ok && t == 0) ok = mbar_wait(bar_kv_full(kslot), kphase, abort_flag, a.status, kDevMmaWaitKV);
                         if (!ok) break;
                         RING_TRACE_STAMP(true, 18 + 4 * t);
-#ifdef RING_DEBUG_LOAD_ONLY
-                        mbar_arrive(bar_kv_empty(kslot));
-                        continue;
-#endif
                         tcgen05_fence_after_thread_sync();
                         issue_qk(t, kslot);
                         umma_commit(bar_s_full(t));
@@ -280,19 +261,13 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         } else if (warp == T::kMmaWarp + 1 || warp == T::kMmaWarp + 2) {
             // =================================================================== UMMA issuer: O_t += P_t V, one warp per tile
             const int t = warp - (T::kMmaWarp + 1);
-            if (lane == 0 && nblk > 0 && t < ntiles && !kSoftmaxOnly) {
+            if (lane == 0 && nblk > 0 && t < ntiles) {
                 // kBlockN/16 instructions of 128 x D x 16, A = 16-bit P in TMEM, B = V MN-major in shared memory
                 bool ok = true;
 #pragma unroll 1
                 for (int j = 0; j < nblk && ok; ++j) {
                     const int vslot = T::kKStages + j % T::kVStages;
                     const uint32_t vphase = static_cast<uint32_t>((j / T::kVStages) & 1);
-#ifdef RING_DEBUG_LOAD_ONLY
-                    ok = mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV);
-                    if (!ok) break;
-                    mbar_arrive(bar_kv_empty(vslot));
-                    continue;
-#endif
                     ok = mbar_wait(bar_p_full(t), j & 1, abort_flag, a.status, kDevMmaWaitP) &&
                          mbar_wait(bar_kv_full(vslot), vphase, abort_flag, a.status, kDevMmaWaitKV);
                     if (!ok) break;
@@ -316,11 +291,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
         setmaxnreg_inc<T::kSoftmaxRegs>();
         const int t = warp >> 2;  // Q tile of this warpgroup
         const int quarter = warp & 3;
-#ifdef RING_DEBUG_NO_SOFTMAX
-        if (false) {
-#else
         if (t < ntiles) {
-#endif
             const int row = r0 + t * 128 + quarter * 32 + lane;  // row of the Q shard == TMEM lane
             const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
             const uint32_t t_s = tmem_base + lane_addr + T::kTmemS;
@@ -336,7 +307,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             for (int j = 0; j < nblk; ++j) {
                 uint32_t sr[128];
                 float* s = reinterpret_cast<float*>(sr);
-                ok = kSoftmaxOnly || mbar_wait(bar_s_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
+                ok = mbar_wait(bar_s_full(t), j & 1, abort_flag, a.status, kDevSoftmaxWaitS);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 RING_TRACE_STAMP(quarter == 0 && lane == 0, t * 8 + 0);
@@ -387,13 +358,6 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                 float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
                 for (int i = 0; i < 128; i += 4) {
-#if RING_POLY_EVERY > 0
-#pragma unroll
-                    for (int u = 0; u < 4; ++u) {
-                        const float x = fmaf(s[i + u], c, nms);
-                        s[i + u] = ((i + u) % RING_POLY_EVERY == RING_POLY_EVERY - 1) ? ex2_poly(x) : ex2_approx(x);
-                    }
-#else
                     // packed fp32 pairs (fma.rn.f32x2 / add.rn.f32x2): same roundings as the scalar forms, half the
                     // issue slots; the S row sits in consecutive registers, so the pairs cost no moves
 #pragma unroll
@@ -403,7 +367,6 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                         s[i + u] = ex2_approx(x0);
                         s[i + u + 1] = ex2_approx(x1);
                     }
-#endif
                     fadd2(a0, a1, a0, a1, s[i], s[i + 1]);
                     fadd2(a2, a3, a2, a3, s[i + 2], s[i + 3]);
                 }
@@ -412,7 +375,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
 
                 // P_t(j - 1) V must be complete before P_t is overwritten or O_t rescaled (it long is)
                 if (j > 0) {
-                    ok = kSoftmaxOnly || mbar_wait(bar_o_done(t), (j - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
+                    ok = mbar_wait(bar_o_done(t), (j - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
                     ok = __all_sync(0xffffffffu, ok);
                     if (!ok) break;
                     tcgen05_fence_after_thread_sync();
@@ -451,7 +414,7 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             RING_TRACE_LIFE(tid == 0, 3);
             // ---- epilogue: O / l, LSE, optional fold into an earlier partial -----------------------
             if (ok && nblk > 0) {
-                ok = kSoftmaxOnly || mbar_wait(bar_o_done(t), (nblk - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
+                ok = mbar_wait(bar_o_done(t), (nblk - 1) & 1, abort_flag, a.status, kDevSoftmaxWaitO);
                 ok = __all_sync(0xffffffffu, ok);
                 if (ok) tcgen05_fence_after_thread_sync();
             }

@@ -65,11 +65,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Makes this thread's earlier generic-proxy writes to shared memory visible to the async proxy
-// (tcgen05.mma / TMA reads of shared memory).
-__device__ __forceinline__ void fence_proxy_async_shared() {
-    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
 __device__ __forceinline__ void st_shared_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -242,34 +237,11 @@ __device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const uint32_t (&r)[
           "r"(r[31])
         : "memory");
 }
-__device__ __forceinline__ void tmem_st_x16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
-          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
-          "r"(r[15])
-        : "memory");
-}
 __device__ __forceinline__ void tmem_wait_ld() {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_wait_st() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// Packed 16-bit pair times a broadcast fp32 factor (factor rounded to the pair's format).
-__device__ __forceinline__ uint32_t scale_f16x2(uint32_t v, float f) {
-    uint32_t ff, r;
-    asm("cvt.rn.f16x2.f32 %0, %1, %1;" : "=r"(ff) : "f"(f));
-    asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(ff));
-    return r;
-}
-__device__ __forceinline__ uint32_t scale_bf16x2(uint32_t v, float f) {
-    uint32_t ff, r;
-    asm("cvt.rn.bf16x2.f32 %0, %1, %1;" : "=r"(ff) : "f"(f));
-    asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(v), "r"(ff));
-    return r;
 }
 
 // Register reallocation between warpgroups (all four warps of the warpgroup must execute it).
@@ -317,21 +289,6 @@ __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
-}
-// 2^x on the FMA pipe (no MUFU): x = n + f with n = round(x), f in [-0.5, 0.5]; 2^f by a degree-4
-// minimax polynomial (relative error < 2.7e-6), 2^n by adding n to the exponent field.
-// Inputs below -125 are clamped (the result, 2^-125, is zero for every purpose here); x must be < 128.
-__device__ __forceinline__ float ex2_poly(float x) {
-    const float kMagic = 12582912.f;  // 1.5 * 2^23: adding it rounds x to the nearest integer in the low mantissa bits
-    x = fmaxf(x, -125.f);
-    const float r = x + kMagic;
-    const float f = x - (r - kMagic);
-    float p = 9.570101276e-03f;
-    p = fmaf(p, f, 5.591785908e-02f);
-    p = fmaf(p, f, 2.402474433e-01f);
-    p = fmaf(p, f, 6.931217909e-01f);
-    p = fmaf(p, f, 9.999992847e-01f);
-    return __int_as_float(__float_as_int(p) + (__float_as_int(r) << 23));
 }
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     uint32_t r;

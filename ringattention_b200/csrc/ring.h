@@ -14,7 +14,7 @@ struct Ring_fwd_params
     int mype;             // this rank
     int npes;             // ring size
     int *seqlen;          // unused by this implementation (the reference keeps a device copy here)
-    int *h_seqlen;        // host: rows held by each rank; all equal (even sharding)
+    int *h_seqlen;        // host: rows held by each rank (they may differ, as the reference's seqlen[] allows)
     int dim;              // head dimension (64 or 128)
     float softmax_scale;  // NATURAL-base scale s: weights = softmax(s * q.k).  (The reference stores 1.0
                           // and feeds it to exp2, csrc/ring_attention.cu:389,597; log2(e) is applied here.)

@@ -8,9 +8,10 @@
 // with these differences: nothing is allocated per call (the reference allocates d_seqlen, k_buffer and
 // v_buffer on every call and never frees them, :384,391,393); run_ring_fwd is the ring loop itself
 // (one block-kernel launch per ring step instead of one kernel looping over PEs, :456) and honours its
-// stream argument (the reference launches on stream 0, :700); the exchange is NCCL send/recv on a side
-// stream into two alternating receive buffers instead of an in-kernel NVSHMEM get into a single buffer
-// (:611-619); errors are returned, not printed-and-exit (csrc/utils.h:1-11).
+// stream argument (the reference launches on stream 0, :700); the exchange runs on a side stream into two
+// alternating receive buffers instead of an in-kernel NVSHMEM get into a single buffer (:611-619), either as
+// copy-engine pushes into the peers' IPC-shared buffers (the default when the ranks can map each other's
+// memory) or as NCCL send/recv; errors are returned, not printed-and-exit (csrc/utils.h:1-11).
 #include <atomic>
 #include <chrono>
 #include <cmath>
@@ -58,9 +59,6 @@ int fail(int code, const char* fmt, ...) {
     } while (0)
 
 std::atomic<int64_t> g_launches{0};
-#ifdef RING_TRACE
-long long* g_trace = nullptr;  // debug builds only
-#endif
 
 // ------------------------------------------------------------------------------------------ NCCL (loaded lazily)
 // The library is usable on one GPU without NCCL being present; multi-rank contexts load it on demand.
@@ -239,13 +237,24 @@ struct BlockLaunch {
     int64_t q_rows_total = 0, k_rows_total = 0;
 };
 
+// What a launch needs from the device it runs on.  The ordinary entry points take it from DeviceState (whose
+// status word is allocated once per device); the no-allocation entry point passes the header of its fixed array.
+struct LaunchEnv {
+    int* status;            // device status word the kernel reports a run-out wait in
+    bool (*attr_set)[2];    // [dim == 128][bf16]: dynamic shared-memory attribute already set on this device
+    int sm_count;
+};
+
 template <class Traits>
-int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t stream) {
+int launch_block_instance(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
     auto kernel = &ring::ring_block_attention_kernel<Traits>;
-    bool& attr = st->attr_set[Traits::kHeadDim == 128][Traits::kIsBf16];
-    if (!attr) {
-        RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
-        attr = true;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        bool& attr = env.attr_set[Traits::kHeadDim == 128][Traits::kIsBf16];
+        if (!attr) {
+            RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
+            attr = true;
+        }
     }
     CUtensorMap tq, tk, tv;
     int rc;
@@ -273,16 +282,13 @@ int launch_block_instance(const BlockLaunch& L, DeviceState* st, cudaStream_t st
     diag = diag > lim ? lim : (diag < -lim ? -lim : diag);
     a.diag = static_cast<int>(diag);
     a.merge = L.merge ? 1 : 0;
-    a.status = st->d_status;
-#ifdef RING_TRACE
-    a.trace = g_trace;
-#endif
+    a.status = env.status;
 
     // Two Q tiles per CTA keep the tensor pipe busiest, but a grid that covers at most half of the SMs that way
     // (one head of a short shard, as in the reference's own driver) finishes sooner with one tile per CTA.
     // (RING_ROWS_PER_CTA = 128 or 256 in the environment overrides the choice; the tests use it to run both forms.)
     a.rows_per_cta = Traits::kBlockM;
-    if (L.sq > 128 && ((L.sq + Traits::kBlockM - 1) / Traits::kBlockM) * L.batch * L.heads * 2 <= st->sm_count) a.rows_per_cta = 128;
+    if (L.sq > 128 && ((L.sq + Traits::kBlockM - 1) / Traits::kBlockM) * L.batch * L.heads * 2 <= env.sm_count) a.rows_per_cta = 128;
     if (const char* e = std::getenv("RING_ROWS_PER_CTA")) {
         const int forced = std::atoi(e);
         if (forced == 128 || forced == Traits::kBlockM) a.rows_per_cta = forced;
@@ -317,28 +323,34 @@ int validate_block(const BlockLaunch& L) {
 
 // Shape dispatch: the reference instantiates Ring_fwd_traits<64, 64, 64, 4, half> only
 // (csrc/ring_attention.cu:707-716); here <64|128, 256, 128, 12, half|bf16>.
+int launch_block_env(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
+    if (L.dim == 128) {
+        if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(L, env, stream);
+        return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __half>>(L, env, stream);
+    }
+    if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<64, 256, 128, 12, __nv_bfloat16>>(L, env, stream);
+    return launch_block_instance<Ring_fwd_traits<64, 256, 128, 12, __half>>(L, env, stream);
+}
+
 int launch_block(const BlockLaunch& L, cudaStream_t stream) {
     int rc = validate_block(L);
     if (rc) return rc;
     DeviceState* st = nullptr;
     if ((rc = device_state(&st))) return rc;
-    if (L.dim == 128) {
-        if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(L, st, stream);
-        return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __half>>(L, st, stream);
-    }
-    if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<64, 256, 128, 12, __nv_bfloat16>>(L, st, stream);
-    return launch_block_instance<Ring_fwd_traits<64, 256, 128, 12, __half>>(L, st, stream);
+    return launch_block_env(L, LaunchEnv{st->d_status, st->attr_set, st->sm_count}, stream);
 }
 
 int launch_merge(float* o_acc, float* lse_acc, const float* o_part, const float* lse_part, int64_t rows, int dim,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, int sms = 0) {
     if (!o_acc || !lse_acc || !o_part || !lse_part) return fail(RING_ERR_INVALID_ARGUMENT, "null tensor pointer");
     if (dim != 64 && dim != 128) return fail(RING_ERR_INVALID_ARGUMENT, "dim must be 64 or 128, got %d", dim);
     if (rows < 0) return fail(RING_ERR_INVALID_ARGUMENT, "negative row count");
     if (rows == 0) return RING_OK;
-    int dev = 0, sms = 148;
-    RING_CUDA(cudaGetDevice(&dev));
-    RING_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    if (sms <= 0) {
+        int dev = 0;
+        RING_CUDA(cudaGetDevice(&dev));
+        RING_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    }
     const int threads = 256;
     const int64_t want = (rows + 7) / 8;              // 8 warps (rows) per block
     const int64_t cap = static_cast<int64_t>(sms) * 8;  // 8 resident blocks per SM, grid-stride beyond that
@@ -376,6 +388,7 @@ struct RingCtx {
     cudaEvent_t ev_fork = nullptr;
     cudaEvent_t ev_recv_done[kMaxWorld] = {};
     cudaEvent_t ev_comm_start[kMaxWorld] = {};
+    cudaEvent_t ev_copy_start[kMaxWorld] = {};  // after the exchange's wait for its go-ahead (credit flag / previous compute)
     cudaEvent_t ev_compute_start[kMaxWorld] = {};
     cudaEvent_t ev_compute_done[kMaxWorld] = {};
     // receive double buffer: recv[i] holds K then V of one shard
@@ -416,6 +429,7 @@ struct RingCtx {
     cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
     cudaEvent_t ev_h2d[kMaxWorld] = {}, ev_comp[kMaxWorld] = {}, ev_d2h[kMaxWorld] = {};
     bool host_ready = false;
+    bool dead = false;  // ring_ctx_abort() was called: forwards are refused, destroy does not wait for the device
 };
 
 constexpr int kFlagReady = 0;
@@ -439,6 +453,7 @@ int ctx_common_init(RingCtx* c) {
     for (int i = 0; i < c->world; ++i) {
         RING_CUDA(cudaEventCreate(&c->ev_recv_done[i]));
         RING_CUDA(cudaEventCreate(&c->ev_comm_start[i]));
+        RING_CUDA(cudaEventCreate(&c->ev_copy_start[i]));
         RING_CUDA(cudaEventCreate(&c->ev_compute_start[i]));
         RING_CUDA(cudaEventCreate(&c->ev_compute_done[i]));
     }
@@ -536,6 +551,13 @@ int peer_grow_recv(RingCtx* c, size_t half_bytes) {
     std::vector<char> all;
     char blob[kXchgBlob] = {0};
     RING_CUDA(cudaDeviceSynchronize());
+    if (!c->recv_block) {  // buffers an earlier NCCL-transport forward obtained with grow(): not shared, release them
+        for (int i = 0; i < 2; ++i) {
+            if (c->recv[i]) RING_CUDA(cudaFree(c->recv[i]));
+            c->recv[i] = nullptr;
+            c->recv_cap[i] = 0;
+        }
+    }
     for (int r = 0; r < c->world; ++r) {  // drop the mappings of the buffers that are about to be freed
         if (r != c->rank && c->peer_recv_block[r]) RING_CUDA(cudaIpcCloseMemHandle(c->peer_recv_block[r]));
         c->peer_recv_block[r] = nullptr;
@@ -711,8 +733,9 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             const int ndst = plan.send_to;    // who gets this rank's shard
             const bool do_recv = plan.do_recv != 0;
             const bool do_send = plan.do_send != 0;
-            if (s >= 2 && !peer) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
             if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_comm_start[s], c->comm_stream));
+            if (s >= 2 && !peer) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
+            if (c->record_timings && !peer) RING_CUDA(cudaEventRecord(c->ev_copy_start[s], c->comm_stream));
             char* dst_k = static_cast<char*>(c->recv[plan.recv_buffer]);
             char* dst_v = dst_k + max_shard_bytes;
             const size_t in_bytes = bytes_of(nsrc);
@@ -720,10 +743,13 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
                 if (do_send) {
                     CUstream cs = reinterpret_cast<CUstream>(c->comm_stream);
                     RING_CU(ops.wait(cs, reinterpret_cast<CUdeviceptr>(c->flags + kFlagCredit + s), seq, CU_STREAM_WAIT_VALUE_GEQ));
+                    if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_copy_start[s], c->comm_stream));
                     char* remote = static_cast<char*>(c->peer_recv_block[ndst]) + plan.recv_buffer * c->peer_recv_half[ndst];
                     RING_CUDA(cudaMemcpyAsync(remote, p.k_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                     RING_CUDA(cudaMemcpyAsync(remote + max_shard_bytes, p.v_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                     RING_CU(ops.write(cs, reinterpret_cast<CUdeviceptr>(c->peer_flags[ndst] + kFlagReady + s), seq, 0));
+                } else if (c->record_timings) {
+                    RING_CUDA(cudaEventRecord(c->ev_copy_start[s], c->comm_stream));
                 }
             } else if (c->local) {
                 if (do_recv) {
@@ -733,17 +759,22 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
                     RING_CUDA(cudaMemcpyAsync(dst_v, c->local_v[nsrc], in_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                 }
             } else if (do_recv || do_send) {
+                // The group is closed on every path: an error between GroupStart and GroupEnd must not leave this
+                // thread inside an open NCCL group.
                 NcclApi& n = nccl();
                 RING_NCCL(n.GroupStart());
+                ncclResult_t gr = ncclSuccess;
                 if (do_send) {
-                    RING_NCCL(n.Send(p.k_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream));
-                    RING_NCCL(n.Send(p.v_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream));
+                    gr = n.Send(p.k_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream);
+                    if (gr == ncclSuccess) gr = n.Send(p.v_ptr, shard_bytes, ncclInt8, ndst, c->comm, c->comm_stream);
                 }
-                if (do_recv) {
-                    RING_NCCL(n.Recv(dst_k, in_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
-                    RING_NCCL(n.Recv(dst_v, in_bytes, ncclInt8, nsrc, c->comm, c->comm_stream));
+                if (do_recv && gr == ncclSuccess) {
+                    gr = n.Recv(dst_k, in_bytes, ncclInt8, nsrc, c->comm, c->comm_stream);
+                    if (gr == ncclSuccess) gr = n.Recv(dst_v, in_bytes, ncclInt8, nsrc, c->comm, c->comm_stream);
                 }
-                RING_NCCL(n.GroupEnd());
+                const ncclResult_t ge = n.GroupEnd();
+                RING_NCCL(gr);
+                RING_NCCL(ge);
             }
             c->step_exchanged[s] = do_recv || do_send;
             RING_CUDA(cudaEventRecord(c->ev_recv_done[s], c->comm_stream));
@@ -845,6 +876,7 @@ namespace {
 
 int validate_params(RingCtx* c, const Ring_fwd_params* p) {
     if (!c) return fail(RING_ERR_INVALID_ARGUMENT, "null context");
+    if (c->dead) return fail(RING_ERR_UNSUPPORTED, "the context was aborted (ring_ctx_abort); destroy it and create a new one");
     if (!p) return fail(RING_ERR_INVALID_ARGUMENT, "null params");
     if (!p->q_ptr || !p->k_ptr || !p->v_ptr || !p->out_ptr) return fail(RING_ERR_INVALID_ARGUMENT, "null tensor pointer");
     if (p->npes != c->world)
@@ -947,10 +979,10 @@ int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id) {
     c->rank = rank;
     c->world = world;
     int rc = ctx_common_init(c);
-    if (rc) { delete c; return rc; }
+    if (rc) { const std::string msg = g_last_error; ring_ctx_destroy(c); g_last_error = msg; return rc; }
     if (world > 1) {
         NcclApi& n = nccl();
-        if (!n.ok) { delete c; return fail(RING_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
+        if (!n.ok) { ring_ctx_destroy(c); return fail(RING_ERR_NCCL, "libnccl.so.2 could not be loaded"); }
         ncclUniqueId id;
         std::memcpy(&id, unique_id, sizeof(id));
         // The exchange only has to keep pace with the block kernel (one K/V shard per ring step), not to
@@ -968,7 +1000,8 @@ int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id) {
             r = n.CommInitRank(&c->comm, world, id, rank);
         }
         if (r != ncclSuccess) {
-            delete c;
+            c->comm = nullptr;
+            ring_ctx_destroy(c);
             return fail(RING_ERR_NCCL, "ncclCommInitRank failed: %s", n.GetErrorString(r));
         }
         // Peer-copy transport: share the flag blocks now (collective); fall back to NCCL send/recv if the
@@ -977,7 +1010,7 @@ int ring_ctx_create(RingCtx** ctx, int rank, int world, const void* unique_id) {
         const bool force_nccl = want && std::strcmp(want, "nccl") == 0;
         if (!force_nccl) {
             rc = peer_setup_flags(c);
-            if (rc) { ring_ctx_destroy(c); return rc; }
+            if (rc) { const std::string msg = g_last_error; ring_ctx_destroy(c); g_last_error = msg; return rc; }
             c->transport = c->peer_ready ? RING_TRANSPORT_PEER_COPY : RING_TRANSPORT_NCCL;
             if (!c->peer_ready && want && std::strcmp(want, "peer") == 0) {
                 ring_ctx_destroy(c);
@@ -998,7 +1031,7 @@ int ring_ctx_create_local(RingCtx** ctx, int world) {
     c->world = world;
     c->local = true;
     int rc = ctx_common_init(c);
-    if (rc) { delete c; return rc; }
+    if (rc) { const std::string msg = g_last_error; ring_ctx_destroy(c); g_last_error = msg; return rc; }
     *ctx = c;
     return RING_OK;
 }
@@ -1057,11 +1090,27 @@ int ring_ctx_get_option(RingCtx* ctx, int option, int* value) {
 int ring_ctx_destroy(RingCtx* c) {
     if (!c) return RING_OK;
     if (g_default_ctx == c) g_default_ctx = nullptr;
-    cudaDeviceSynchronize();
+    if (g_solo_ctx == c) g_solo_ctx = nullptr;
+    // An aborted context has released every wait it had queued (ring_ctx_abort) and its communicator is gone;
+    // waiting for the device here could block on whatever made the caller abort.
+    if (!c->dead) {
+        cudaDeviceSynchronize();
+    } else {
+        // give the released work a bounded time to drain before its buffers go away
+        const auto deadline = std::chrono::steady_clock::now() + std::chrono::seconds(5);
+        while (std::chrono::steady_clock::now() < deadline) {
+            const cudaError_t e1 = c->have_call_done ? cudaEventQuery(c->ev_call_done) : cudaSuccess;
+            const cudaError_t e2 = c->comm_stream ? cudaStreamQuery(c->comm_stream) : cudaSuccess;
+            (void)cudaGetLastError();
+            if (e1 != cudaErrorNotReady && e2 != cudaErrorNotReady) break;
+            std::this_thread::sleep_for(std::chrono::milliseconds(1));
+        }
+    }
     if (c->comm) nccl().CommDestroy(c->comm);
     for (int i = 0; i < c->world; ++i) {
         if (c->ev_recv_done[i]) cudaEventDestroy(c->ev_recv_done[i]);
         if (c->ev_comm_start[i]) cudaEventDestroy(c->ev_comm_start[i]);
+        if (c->ev_copy_start[i]) cudaEventDestroy(c->ev_copy_start[i]);
         if (c->ev_compute_start[i]) cudaEventDestroy(c->ev_compute_start[i]);
         if (c->ev_compute_done[i]) cudaEventDestroy(c->ev_compute_done[i]);
     }
@@ -1224,6 +1273,53 @@ int ring_ctx_synchronize_timeout(RingCtx* ctx, int timeout_ms) {
     return RING_OK;
 }
 
+// Way out after ring_ctx_synchronize_timeout() gave up (a peer stopped, so a queued wait will never be satisfied).
+// Every cross-process wait this context queues is a stream wait on a word of ITS OWN flag block, compared with >=
+// against the call's sequence number (a cyclic comparison, (int32)(word - seq) >= 0): storing a value 2^30 ahead
+// of the current sequence number into every word from the host releases them all, and the queued copies and kernels then drain (into receive buffers that are still mapped -- peers must
+// keep theirs alive until this rank has destroyed its context).  The NCCL communicator is aborted, not destroyed
+// (ncclCommDestroy waits for outstanding operations).  The context is dead afterwards: forwards are refused and
+// ring_ctx_destroy() frees it without a device-wide synchronisation.  Results of the aborted forward are undefined.
+int ring_ctx_abort(RingCtx* c) {
+    if (!c) return fail(RING_ERR_INVALID_ARGUMENT, "null context");
+    if (c->dead) return RING_OK;
+    c->dead = true;
+    if (c->flags) {
+        // The flag block is device memory; the store must not queue behind the stuck streams.  A blocking copy on a
+        // fresh non-blocking stream is independent of them.
+        std::vector<uint32_t> all(2 * kMaxWorld, c->call_seq + 0x40000000u);
+        cudaStream_t s = nullptr;
+        RING_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+        cudaError_t e = cudaMemcpyAsync(c->flags, all.data(), all.size() * sizeof(uint32_t), cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        cudaStreamDestroy(s);
+        RING_CUDA(e);
+    }
+    if (c->comm) {
+        nccl().CommAbort(c->comm);
+        c->comm = nullptr;
+    }
+    return RING_OK;
+}
+
+// The exchange of step i split in two: wait_ms[i] is the time its stream waited for the go-ahead (peer-copy: the
+// destination's credit flag; NCCL: the compute step that last read the receive buffer), copy_ms[i] the transfer
+// itself (for the peer-copy transport: this rank's PUSH of its own shard).  Needs RING_OPT_RECORD_TIMINGS.
+int ring_ctx_get_exchange_timings(RingCtx* c, float* wait_ms, float* copy_ms, int n) {
+    if (!c || !wait_ms || !copy_ms) return fail(RING_ERR_INVALID_ARGUMENT, "null argument");
+    if (!c->record_timings) return fail(RING_ERR_INVALID_ARGUMENT, "RING_OPT_RECORD_TIMINGS is off");
+    if (n < c->last_steps) return fail(RING_ERR_INVALID_ARGUMENT, "arrays too short: %d < %d", n, c->last_steps);
+    const int P = c->last_steps;
+    for (int s = 0; s < P; ++s) {
+        wait_ms[s] = copy_ms[s] = 0.f;
+        if (s < P - 1) {
+            RING_CUDA(cudaEventElapsedTime(&wait_ms[s], c->ev_comm_start[s], c->ev_copy_start[s]));
+            RING_CUDA(cudaEventElapsedTime(&copy_ms[s], c->ev_copy_start[s], c->ev_recv_done[s]));
+        }
+    }
+    return RING_OK;
+}
+
 int ring_ctx_get_timings(RingCtx* c, float* compute_ms, float* comm_ms, float* exposed_ms, int n) {
     if (!c || !compute_ms || !comm_ms || !exposed_ms) return fail(RING_ERR_INVALID_ARGUMENT, "null argument");
     if (!c->record_timings) return fail(RING_ERR_INVALID_ARGUMENT, "RING_OPT_RECORD_TIMINGS is off");
@@ -1309,11 +1405,13 @@ namespace {
 struct StaticSetup {
     float* base = nullptr;  // DEVICE address of g_static_scratch on this device (the symbol itself is a host-side stand-in)
     bool attr_set[2][2] = {{false, false}, {false, false}};
+    int sm_count = 0;
 };
 std::mutex g_static_mutex;
 StaticSetup g_static[64];
 
-// Once per device, with that device current: resolve the device address of the array.
+// Once per device, with that device current: resolve the device address of the array and read the SM count
+// (neither call allocates).
 int static_setup(StaticSetup** out) {
     int dev = 0;
     RING_CUDA(cudaGetDevice(&dev));
@@ -1324,82 +1422,10 @@ int static_setup(StaticSetup** out) {
         void* p = nullptr;
         RING_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
         if (!p) return fail(RING_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+        RING_CUDA(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev));
         s.base = static_cast<float*>(p);
     }
     *out = &s;
-    return RING_OK;
-}
-
-// Tensor map over `rows` rows of a [batch, heads, rows_total, dim] tensor starting at `base` (which may
-// point into the middle of the sequence): the head and batch strides are those of the whole tensor.
-int make_tensor_map_strided(CUtensorMap* tm, const void* base, int batch, int heads, int rows, int64_t rows_total, int dim,
-                            bool bf16) {
-    EncodeTiledFn enc = nullptr;
-    int rc = encode_fn(&enc);
-    if (rc) return rc;
-    const cuuint64_t dims[4] = {static_cast<cuuint64_t>(dim), static_cast<cuuint64_t>(rows),
-                                static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
-    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(rows_total) * dim * 2,
-                                   static_cast<cuuint64_t>(heads) * rows_total * dim * 2};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
-    const cuuint32_t estr[4] = {1, 1, 1, 1};
-    CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
-                     const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(RING_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-    return RING_OK;
-}
-
-struct StaticChunk {
-    const void *q, *k, *v;  // k, v already advanced to the first row of the chunk
-    float* o;
-    float* lse;
-    int batch, heads, sq, sk_total, rows, dim;
-    float scale;
-    int causal;
-    int64_t k_off;
-    int is_bf16;
-};
-
-template <class Traits>
-int launch_block_static(const StaticChunk& c, StaticSetup* s, cudaStream_t stream) {
-    auto kernel = &ring::ring_block_attention_kernel<Traits>;
-    bool& attr = s->attr_set[Traits::kHeadDim == 128][Traits::kIsBf16];
-    if (!attr) {
-        RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
-        attr = true;
-    }
-    CUtensorMap tq, tk, tv;
-    int rc;
-    if ((rc = make_tensor_map_strided(&tq, c.q, c.batch, c.heads, c.sq, c.sq, c.dim, c.is_bf16))) return rc;
-    if ((rc = make_tensor_map_strided(&tk, c.k, c.batch, c.heads, c.rows, c.sk_total, c.dim, c.is_bf16))) return rc;
-    if ((rc = make_tensor_map_strided(&tv, c.v, c.batch, c.heads, c.rows, c.sk_total, c.dim, c.is_bf16))) return rc;
-    ring::BlockFwdArgs a;
-    a.o = c.o;
-    a.lse = c.lse;
-    a.o_row_stride = c.dim;
-    a.o_head_stride = static_cast<int64_t>(c.sq) * c.dim;
-    a.o_batch_stride = a.o_head_stride * c.heads;
-    a.lse_head_stride = c.sq;
-    a.lse_batch_stride = static_cast<int64_t>(c.sq) * c.heads;
-    a.heads = c.heads;
-    a.sq = c.sq;
-    a.sk = c.rows;
-    a.scale = c.scale;
-    a.scale_log2 = c.scale * 1.4426950408889634f;
-    a.causal = c.causal ? 1 : 0;
-    a.diag = static_cast<int>(-c.k_off);
-    a.merge = 0;
-    a.status = reinterpret_cast<int*>(s->base);  // header word 0
-#ifdef RING_TRACE
-    a.trace = nullptr;
-#endif
-    a.rows_per_cta = Traits::kBlockM;
-    dim3 grid((c.sq + Traits::kBlockM - 1) / Traits::kBlockM, c.batch * c.heads);
-    kernel<<<grid, dim3(Traits::kNThreads), Traits::kSmemSize, stream>>>(tq, tk, tv, a);
-    RING_CUDA(cudaGetLastError());
-    g_launches.fetch_add(1, std::memory_order_relaxed);
     return RING_OK;
 }
 
@@ -1433,40 +1459,29 @@ extern "C" int ring_attention_chunked_fwd_static(const void* q, const void* k, c
     // block kernel before the merge reads it.
     RING_CUDA(cudaMemsetAsync(s->base, 0, sizeof(int), stream));
 
+    const LaunchEnv env{reinterpret_cast<int*>(s->base) /* header word 0 */, s->attr_set, s->sm_count};
     for (int c0 = 0; c0 < sk; c0 += kv_chunk) {
-        StaticChunk c;
-        c.q = q;
-        c.k = static_cast<const char*>(k) + static_cast<size_t>(c0) * dim * 2;
-        c.v = static_cast<const char*>(v) + static_cast<size_t>(c0) * dim * 2;
-        c.batch = batch; c.heads = heads; c.sq = sq; c.sk_total = sk;
-        c.rows = (sk - c0) < kv_chunk ? (sk - c0) : kv_chunk;
-        c.dim = dim; c.scale = softmax_scale; c.causal = causal; c.k_off = c0; c.is_bf16 = is_bf16;
-        c.o = c0 == 0 ? o : o_part;
-        c.lse = c0 == 0 ? lse : lse_part;
-        if (dim == 128) {
-            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(c, s, stream)
-                         : launch_block_static<Ring_fwd_traits<128, 256, 128, 12, __half>>(c, s, stream);
-        } else {
-            rc = is_bf16 ? launch_block_static<Ring_fwd_traits<64, 256, 128, 12, __nv_bfloat16>>(c, s, stream)
-                         : launch_block_static<Ring_fwd_traits<64, 256, 128, 12, __half>>(c, s, stream);
-        }
-        if (rc) return rc;
-        if (c0 > 0) {
-            // same grid sizing as launch_merge(), without the device-attribute query
-            const int threads = 256;
-            const int64_t want = (rows + 7) / 8;
-            const int blocks = static_cast<int>(want < 148 * 8 ? want : 148 * 8);
-            if (dim == 128)
-                ring::ring_lse_merge_kernel<128><<<blocks, threads, 0, stream>>>(o, lse, o_part, lse_part, rows);
-            else
-                ring::ring_lse_merge_kernel<64><<<blocks, threads, 0, stream>>>(o, lse, o_part, lse_part, rows);
-            RING_CUDA(cudaGetLastError());
-            g_launches.fetch_add(1, std::memory_order_relaxed);
-        }
+        BlockLaunch L = whole;  // K/V rows [c0, c0 + rows) of every (batch, head) slab of sk rows
+        L.k = static_cast<const char*>(k) + static_cast<size_t>(c0) * dim * 2;
+        L.v = static_cast<const char*>(v) + static_cast<size_t>(c0) * dim * 2;
+        L.sk = (sk - c0) < kv_chunk ? (sk - c0) : kv_chunk;
+        L.k_rows_total = sk;
+        L.k_off = c0;
+        L.o = c0 == 0 ? o : o_part;
+        L.lse = c0 == 0 ? lse : lse_part;
+        if ((rc = launch_block_env(L, env, stream))) return rc;
+        if (c0 > 0 && (rc = launch_merge(o, lse, o_part, lse_part, rows, dim, stream, s->sm_count))) return rc;
     }
     return RING_OK;
 }
 
-#ifdef RING_TRACE
-extern "C" int ring_debug_set_trace(long long* buf) { g_trace = buf; return 0; }
-#endif
+extern "C" int ring_static_status(int* status_out, void* stream_) {
+    if (!status_out) return fail(RING_ERR_INVALID_ARGUMENT, "null status_out");
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+    StaticSetup* s = nullptr;
+    int rc = static_setup(&s);
+    if (rc) return rc;
+    RING_CUDA(cudaMemcpyAsync(status_out, s->base, sizeof(int), cudaMemcpyDeviceToHost, stream));
+    RING_CUDA(cudaStreamSynchronize(stream));
+    return RING_OK;
+}

@@ -11,8 +11,8 @@ them, unmodified, in a namespace whose Q, K, V are CPU tensors:
 The reference has no softmax scale (it is 1).  A scale of 2^-3 is obtained by
 pre-multiplying Q by 0.125 (exactly, in fp64) before the reference statements run.
 
-Run from the repository root (needs the reference checkout; the fixtures travel, it does not):
-    python tests/golden/make_golden.py /root/reference
+Run from the repository root with the path of a checkout of the reference (the fixtures travel, it does not):
+    python tests/golden/make_golden.py <path to ykcombat/RingAttention>
 """
 import os
 import sys
@@ -51,7 +51,9 @@ def run_reference(src: str, Q, K, V):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <path to the reference checkout>")
+    ref_root = sys.argv[1]
     src = reference_statements(ref_root)
     for name, seed, S, D, prescale, gain in CASES:
         q, k, v = synthetic.make_qkv(seed, 1, 1, D, 0, S, gain)

@@ -51,8 +51,6 @@ def test_reference_entry_point_on_golden(ra, path):
     g = np.load(path)
     q, k, v = (to_dev(g[n]) for n in ("q", "k", "v"))
     S, D = g["q"].shape
-    if S % 128 != 0:
-        pytest.skip("fixture length not a multiple of 128")
     out = torch.full((S, D), float("nan"), device="cuda")
     ra.ring_attention_scaled(q, k, v, out, 1, 0, [S], D, S, float(g["scale"]))
     got = out.cpu().numpy()

@@ -3,9 +3,11 @@
 Some hosts give a component its input and output tensors but no way to obtain device memory of its own
 (a serving runtime that reserved the whole GPU, a fixed memory budget).  For them the library keeps the
 scratch of the chunked forward in a fixed device array.  The checks: the result equals the existing
-ring_attention_block_fwd over the whole K/V within the parity bar of this repository, on two calls in a
-row that share the array (second call: other shape, other data, so stale contents would show), and sizes
-beyond the array are refused.  Collected last on purpose (file name), so a failure here cannot hide
+ring_attention_block_fwd over the whole K/V, and the CPU oracle, within the parity bar of this repository,
+on calls in a row that share the array (second call: other shape, other data, so stale contents would
+show); once the first call has done the one-time set-up, a further call leaves the device's free memory
+exactly as it was while the kernel counter rises; the path's own status word reads zero; and sizes beyond
+the array are refused.  Collected last on purpose (file name), so a failure here cannot hide
 another test's result in a run that stops at the first failure.
 """
 import ctypes
@@ -44,10 +46,13 @@ def test_static_scratch_entry_matches_block_forward_twice():
     lib = _lib.load()
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
+    from oracle import oracle
+
     def both(seed, B, H, Sq, Sk, D, chunk, causal):
-        q = torch.from_numpy(synthetic.make_shard("q", seed, B, H, D, 0, Sq)).cuda()
-        k = torch.from_numpy(synthetic.make_shard("k", seed, B, H, D, 0, Sk)).cuda()
-        v = torch.from_numpy(synthetic.make_shard("v", seed, B, H, D, 0, Sk)).cuda()
+        qh = synthetic.make_shard("q", seed, B, H, D, 0, Sq)
+        kh = synthetic.make_shard("k", seed, B, H, D, 0, Sk)
+        vh = synthetic.make_shard("v", seed, B, H, D, 0, Sk)
+        q, k, v = (torch.from_numpy(x).cuda() for x in (qh, kh, vh))
         scale = D ** -0.5
         o_ref = torch.full((B, H, Sq, D), float("nan"), device="cuda")
         l_ref = torch.full((B, H, Sq), float("nan"), device="cuda")
@@ -66,10 +71,34 @@ def test_static_scratch_entry_matches_block_forward_twice():
         assert np.abs(a - b).max() <= TOL_O_MAXABS
         assert np.linalg.norm(a - b) / np.linalg.norm(a) <= TOL_O_RELL2
         assert np.abs(la - lb).max() <= TOL_LSE
+        want_o, want_l = oracle.attention_fwd(qh, kh, vh, scale, causal=causal)   # fp64 accumulation on the CPU
+        assert np.abs(want_o - b).max() <= TOL_O_MAXABS
+        assert np.linalg.norm(want_o - b) / np.linalg.norm(want_o) <= TOL_O_RELL2
+        assert np.abs(want_l - lb).max() <= TOL_LSE
+        st = ctypes.c_int(-1)
+        assert lib.ring_static_status(ctypes.byref(st), stream) == 0 and st.value == 0   # the word THIS path writes
 
     # two calls in a row through the same fixed array: different shapes, data, chunking and masks
     both(501, 1, 4, 512, 1024, 128, 256, False)
     both(502, 2, 2, 256, 640, 64, 256, True)      # last chunk shorter than the others
     both(501, 1, 4, 512, 1024, 128, 1024, False)  # single chunk: scratch untouched, still equal
-    status = ctypes.c_int(-1)
-    assert lib.ring_device_status(ctypes.byref(status)) == 0 and status.value == 0
+
+    # Set-up is done (every head dimension used below has run once): one more call must not change the device's
+    # free memory by a byte, although it launches kernels.  Inputs and outputs are made before the measurement.
+    B, H, Sq, Sk, D = 1, 4, 512, 1024, 128
+    q = torch.from_numpy(synthetic.make_shard("q", 503, B, H, D, 0, Sq)).cuda()
+    k = torch.from_numpy(synthetic.make_shard("k", 503, B, H, D, 0, Sk)).cuda()
+    v = torch.from_numpy(synthetic.make_shard("v", 503, B, H, D, 0, Sk)).cuda()
+    o = torch.empty((B, H, Sq, D), device="cuda")
+    l = torch.empty((B, H, Sq), device="cuda")
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    launches0 = lib.ring_kernel_launch_count()
+    rc = lib.ring_attention_chunked_fwd_static(q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(), l.data_ptr(),
+                                               B, H, Sq, Sk, D, D ** -0.5, 0, 256, 0, stream)
+    assert rc == 0, lib.ring_last_error_string()
+    st = ctypes.c_int(-1)
+    assert lib.ring_static_status(ctypes.byref(st), stream) == 0 and st.value == 0
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, f"device free memory changed by {free0 - free1} bytes across a call"
+    assert lib.ring_kernel_launch_count() - launches0 == 4 + 3   # four chunks, three merges
