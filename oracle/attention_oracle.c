@@ -68,15 +68,33 @@ static float h2f_slow(uint16_t h) {
     return f;
 }
 
+/* Input format of the 16-bit tensors: 0 = fp16 (the reference's FPC = cute::half_t, csrc/ring_attention.cu:18),
+ * 1 = bf16 (csrc/kernel_traits.h:27-30 anticipates it).  Both widen exactly to fp32 through one table; every
+ * function below is the same code after the widening.  Set from one thread, between calls. */
+static int h2f_want_bf16 = 0;
+
 static void h2f_init(void) {
-    if (h2f_ready) return;
+    if (h2f_ready == 1 + h2f_want_bf16) return;
 #pragma omp critical(h2f_init_lock)
     {
-        if (!h2f_ready) {
-            for (uint32_t i = 0; i < 65536u; ++i) h2f_table[i] = h2f_slow((uint16_t)i);
-            h2f_ready = 1;
+        if (h2f_ready != 1 + h2f_want_bf16) {
+            for (uint32_t i = 0; i < 65536u; ++i) {
+                if (h2f_want_bf16) {
+                    uint32_t bits = i << 16; /* bf16 is the upper half of the fp32 encoding */
+                    memcpy(&h2f_table[i], &bits, 4);
+                } else {
+                    h2f_table[i] = h2f_slow((uint16_t)i);
+                }
+            }
+            h2f_ready = 1 + h2f_want_bf16;
         }
     }
+}
+
+int oracle_set_input_bf16(int on) {
+    h2f_want_bf16 = on ? 1 : 0;
+    h2f_init();
+    return 0;
 }
 
 static void widen_f32(const uint16_t* src, float* dst, size_t n) {
@@ -462,6 +480,18 @@ int oracle_num_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
 #else
+    return 1;
+#endif
+}
+
+/* Launchers such as torchrun export OMP_NUM_THREADS=1 to their workers; the timed CPU baseline asks for the
+ * host's cores explicitly.  n <= 0 leaves the runtime's choice. */
+int oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
     return 1;
 #endif
 }

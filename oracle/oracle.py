@@ -48,6 +48,10 @@ def lib() -> ctypes.CDLL:
         L.oracle_ring_attention_fwd.restype = i32
         L.oracle_fill_with_num.argtypes = [u16p, i64, i64]
         L.oracle_fill_with_num.restype = i32
+        L.oracle_set_input_bf16.argtypes = [i32]
+        L.oracle_set_input_bf16.restype = i32
+        L.oracle_set_num_threads.argtypes = [i32]
+        L.oracle_set_num_threads.restype = i32
         L.oracle_num_threads.argtypes = []
         L.oracle_num_threads.restype = i32
         _lib = L
@@ -55,8 +59,22 @@ def lib() -> ctypes.CDLL:
 
 
 def _u16(a: np.ndarray):
-    assert a.dtype == np.float16 and a.flags["C_CONTIGUOUS"]
+    """fp16 arrays, or uint16 arrays holding bf16 bit patterns (numpy has no bf16 type)."""
+    assert a.dtype in (np.float16, np.uint16) and a.flags["C_CONTIGUOUS"]
+    lib().oracle_set_input_bf16(1 if a.dtype == np.uint16 else 0)
     return a.view(np.uint16).ctypes.data_as(ctypes.POINTER(ctypes.c_uint16))
+
+
+def to_bf16_bits(x: np.ndarray) -> np.ndarray:
+    """Round fp32 values to bf16 (nearest even) and return the bit patterns as uint16: the form in which
+    the functions of this module take bf16 inputs (q, k and v must then all be uint16)."""
+    b = np.ascontiguousarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    b = (b + 0x7FFF + ((b >> 16) & 1)) >> 16
+    return b.astype(np.uint16)
+
+
+def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
 
 
 def _f32(a: np.ndarray):
@@ -132,6 +150,11 @@ def fill_with_num(m, n):
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """Ask OpenMP for n threads whatever OMP_NUM_THREADS says (torchrun exports 1); returns the count in use."""
+    return int(lib().oracle_set_num_threads(int(n)))
 
 
 def attention_numpy(q, k, v, scale, causal=False, q_off=0, k_off=0):

@@ -187,22 +187,6 @@ def test_lse_merge_kernel_vs_oracle(ra, D):
     assert np.all(got_o[~fin] == 0)
 
 
-def test_bf16_inputs(ra):
-    import torch
-    B, H, S, D = 1, 2, 256, 128
-    q, k, v = synthetic.make_qkv(91, B, H, D, 0, S)
-    tq, tk, tv = (torch.from_numpy(x.astype(np.float32)).to(torch.bfloat16).cuda() for x in (q, k, v))
-    o = torch.empty((B, H, S, D), device="cuda"); lse = torch.empty((B, H, S), device="cuda")
-    ra.attention_block_fwd(tq, tk, tv, o, lse, softmax_scale=D ** -0.5)
-    f = lambda t: t.float().double()
-    s = torch.einsum("bhid,bhjd->bhij", f(tq), f(tk)) * D ** -0.5
-    want = torch.einsum("bhij,bhjd->bhid", torch.softmax(s, -1), f(tv)).float().cpu().numpy()
-    want_l = torch.logsumexp(s, -1).float().cpu().numpy()
-    # bf16 P carries 8 mantissa bits: looser O bound, same LSE bound
-    assert np.abs(o.cpu().numpy() - want).max() <= 1.5e-2
-    assert np.abs(lse.cpu().numpy() - want_l).max() <= 1e-4
-
-
 def test_same_inputs_same_bits(ra):
     """Run-to-run determinism (no atomics, fixed accumulation order)."""
     B, H, S, D = 1, 4, 512, 128

@@ -89,3 +89,44 @@ def test_host_deadline_notices_a_forward_that_does_not_finish():
     assert np.abs(out.cpu().numpy() - want_o).max() <= 2e-3
     assert np.abs(lse.cpu().numpy() - want_lse).max() <= 1e-4
     ctx.destroy()
+
+
+def test_abort_after_host_timeout_lets_the_context_go():
+    """The way out after a detected failure: a forward sits behind a stream wait nothing satisfies (a stopped peer,
+    seen from this rank); synchronize(timeout) reports it; abort() marks the context dead, further forwards are
+    refused, and destroy() comes back within its own bounded drain instead of blocking on the device.  The flag is
+    written afterwards, so nothing is left waiting on the GPU when the test ends."""
+    import time
+
+    import torch
+    import ringattention_b200 as ra
+    from cuda.bindings import driver
+
+    B, H, S, D = 1, 2, 256, 64
+    q, k, v = (to_dev(x) for x in synthetic.make_qkv(22, B, H, D, 0, S))
+    out = torch.zeros((B, H, S, D), device="cuda")
+    lse = torch.zeros((B, H, S), device="cuda")
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ra.device_status_reset()
+    ctx = ra.RingContext.create(0, 1, None)
+    work, side = torch.cuda.Stream(), torch.cuda.Stream()
+    torch.cuda.synchronize()
+    try:
+        (err,) = driver.cuStreamWaitValue32(work.cuda_stream, flag.data_ptr(), 1, driver.CUstreamWaitValue_flags.CU_STREAM_WAIT_VALUE_GEQ)
+        assert int(err) == 0
+        ctx.forward(q, k, v, out, lse, stream=work.cuda_stream)
+        with pytest.raises(ra.RingError) as e:
+            ctx.synchronize(timeout_ms=200)
+        assert e.value.code == ra.RING_ERR_HOST_TIMEOUT
+        ctx.abort()
+        with pytest.raises(ra.RingError) as e:
+            ctx.forward(q, k, v, out, lse, stream=work.cuda_stream)
+        assert e.value.code == _lib.RING_ERR_UNSUPPORTED and "aborted" in str(e.value)
+        t0 = time.perf_counter()
+        ctx.destroy()                       # must not wait for the stream that is still held
+        assert time.perf_counter() - t0 <= 8.0
+    finally:
+        with torch.cuda.stream(side):
+            flag.fill_(1)
+        torch.cuda.synchronize()
+    assert ra.device_status() == 0

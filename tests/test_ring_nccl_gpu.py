@@ -49,6 +49,18 @@ def test_ring_small(world, config, merge_mode, transport, tmp_path):
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+@pytest.mark.parametrize("config", ["uneven", "uneven_causal", "bf16", "bf16_causal_d64"])
+def test_ring_uneven_shards_and_bf16(world, config, transport, tmp_path):
+    """Shards of different lengths per rank (the receive layout is sized for the longest) and bf16 inputs, on real
+    ranks, for both transports."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    r = _run(world, config, 1, tmp_path, transport=transport)
+    assert r["transport"] == transport
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
 def test_ring_small_zigzag(world, tmp_path):
     if _gpus() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -61,3 +73,39 @@ def test_nccl_ring_baseline_configs(config, world, tmp_path):
         pytest.skip(f"needs {world} GPUs")
     r = _run(world, config, 1, tmp_path)
     print(json.dumps(r))
+
+
+def test_reference_driver_two_pes(tmp_path):
+    """The reference's own experiment (`nvshmrun -n 2 build/ring_attention`, makefile:1-2; main,
+    csrc/ring_attention.cu:750-790) with this library's driver executable: two processes, one GPU each, every PE
+    holding the same deterministic fill; rank 0's 8x8 corner must be the attention of its Q over the 2 x S rows."""
+    import numpy as np
+    from oracle import oracle
+    if _gpus() < 2:
+        pytest.skip("needs 2 GPUs")
+    exe = os.path.join(ROOT, "ringattention_b200", "ring_attention_main")
+    S = 1024
+    idf = os.path.join(str(tmp_path), "ring_id")
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RING_SEQ=str(S), RING_WARMUP="2", RING_LOOPS="3", RING_WORLD="2", RING_RANK=str(r),
+                   RING_ID_FILE=idf, NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([exe], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = []
+    for p in procs:
+        try:
+            o, e = p.communicate(timeout=300)
+        except subprocess.TimeoutExpired:
+            for x in procs:
+                x.kill()          # the exact processes this test started
+            raise
+        assert p.returncode == 0, o + e
+        outs.append(o)
+    lines = outs[0].strip().splitlines()
+    assert lines[0] == "mype: 0 success" and lines[-1].startswith("elapsedtime=")
+    assert outs[1].strip().splitlines()[0] == "mype: 1 success"
+    corner = np.array([[float(x) for x in ln.split()] for ln in lines[1:9]], dtype=np.float32)
+    f = oracle.fill_with_num(S, 64)
+    kv = np.concatenate([f, f], axis=0)[None, None]
+    want, _ = oracle.attention_fwd(f[None, None], kv, kv, 64 ** -0.5)
+    assert np.abs(corner - want[0, 0, :8, :8]).max() <= 2e-3 * max(1.0, float(np.abs(want).max()))
