@@ -542,10 +542,24 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
     buf_a = torch.empty(int(kv_bytes), dtype=torch.uint8, device=dev)
     buf_b = torch.empty_like(buf_a)
     probe = {"plain": [], "merge": [], "copies": []}
+    probe_mhz = {"plain": [], "merge": [], "copies": []}
+
+    def probed(name, **kw):
+        # SM clock sampled while the batch runs: time x clock tells a slower kernel (more clocks) from a lower clock
+        # (the power cap answering extra memory traffic)
+        smp = ClockSampler(local_rank)
+        if rank == 0:
+            smp.start()
+        probe[name].append(k1_time(n=40, **kw))
+        if rank == 0:
+            mhz = smp.stop().get("sm_mhz")
+            if mhz:
+                probe_mhz[name].append(mhz)
+
     for _ in range(4):
-        probe["plain"].append(k1_time(n=15))
-        probe["merge"].append(k1_time(merge=True, n=15))
-        probe["copies"].append(k1_time(side_copies=(side, buf_a, buf_b), n=15))
+        probed("plain")
+        probed("merge", merge=True)
+        probed("copies", side_copies=(side, buf_a, buf_b))
     del buf_a, buf_b
     # the library GEMM the roofline's denominator was measured with, under the same power-steady protocol, same run
     ga = torch.randn(8192, 8192, device=dev, dtype=torch.bfloat16)
@@ -686,9 +700,12 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
                                                                 "ratio": k1_flops / (k1_burst_ms * 1e-3) / 1e12 / cublas_burst_tflops}}},
             "k1_probes": {"what": "block kernel alone, ms per launch (rank 0), same shape as one ring step of the headline",
                           "before_any_ring_step": k1_before_ms, "after_timed_region": k1_ms,
-                          "interleaved_batches_of_15": {"plain": probe["plain"], "folding_into_partial": probe["merge"],
+                          "interleaved_batches_of_40": {"plain": probe["plain"], "folding_into_partial": probe["merge"],
                                                         "with_two_d2d_copies_of_a_kv_shard_per_launch": probe["copies"]},
-                          "median": {kk: statistics.median(vv) for kk, vv in probe.items()}},
+                          "median_ms": {kk: statistics.median(vv) for kk, vv in probe.items()},
+                          "median_sm_mhz": {kk: (statistics.median(vv) if vv else None) for kk, vv in probe_mhz.items()},
+                          "median_ms_x_sm_ghz": {kk: (statistics.median(probe[kk]) * statistics.median(vv) / 1e3 if vv else None)
+                                                 for kk, vv in probe_mhz.items()}},
             "merge_kernel": {"bound": "hbm", "achieved": k2_bytes / (k2_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                              "frac": k2_bytes / (k2_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "ms_per_launch": k2_ms},
             "exchange": exchange,

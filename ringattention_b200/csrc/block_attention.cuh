@@ -54,6 +54,7 @@ enum DeviceStatus : int {
     kDevMmaWaitS = 114,
     kDevSoftmaxWaitS = 121,
     kDevSoftmaxWaitO = 122,
+    kDevSoftmaxWaitM = 123,  // pair form: the row maximum handed over by the other warpgroup
 };
 
 struct BlockFwdArgs {

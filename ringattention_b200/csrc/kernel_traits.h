@@ -80,3 +80,61 @@ struct Ring_fwd_traits : public Base
     static constexpr int kTmemO0 = kBlockN + kQTiles * kTmemPCols;  // O tile t at kTmemO0 + t*kHeadDim
     static_assert(kTmemO0 + kQTiles * kHeadDim <= kTmemCols, "TMEM budget");
 };
+
+// Shape configuration of the CTA-PAIR form of the block-attention kernel (head dimension 128).
+//
+// Two CTAs of a cluster own 128 Q rows each and walk the K/V shard together: every tcgen05.mma is a cta_group::2
+// instruction of M = 256 whose B operand is split between the two CTAs' shared memories, so each CTA loads only
+// half of every K block (64 keys) and half of every V block (64 of the 128 value columns).  Per CTA that is the
+// K/V stream of a 256-row CTA, which leaves shared memory for deep K/V rings and, with one Q tile instead of two,
+// tensor memory for TWO S buffers: S of block j + 1 is computed while block j is still in its softmax.
+// Same constant names as Ring_fwd_traits where they mean the same thing.
+template <int kHeadDim_, typename elem_type = __half, typename Base = Ring_kernel_traits<kHeadDim_, 128, 128, 12, elem_type>>
+struct Ring_pair_traits : public Base
+{
+    using Element = typename Base::Element;
+    using ElementAccum = typename Base::ElementAccum;
+    using index_t = typename Base::index_t;
+
+    static constexpr int kNWarps = 12;
+    static constexpr int kNThreads = kNWarps * 32;
+    static constexpr int kBlockM = 128;        // Q rows per CTA (256 per pair)
+    static constexpr int kBlockN = 128;        // K/V rows per block (64 of them, or 64 value columns, per CTA)
+    static constexpr int kHeadDim = kHeadDim_;
+    static_assert(kHeadDim == 128, "the pair form is instantiated for head dimension 128");
+
+    // warps 0-3 / 4-7: softmax warpgroups of the even / odd K/V blocks (one thread per Q row in each);
+    // warp 8: TMEM allocation, and in the leader CTA the issuer of S = Q K^T; warp 9 (leader): issuer of O += P V;
+    // warp 10: TMA loads of V; warp 11: TMA loads of Q and K (K slots are released early, V slots late: one thread
+    // for both would hold the K loads back behind a V slot that is still being read).
+    static constexpr int kSoftmaxWarps = 8;
+    static constexpr int kQkWarp = 8;
+    static constexpr int kPvWarp = 9;
+    static constexpr int kLoadWarpV = 10;
+    static constexpr int kLoadWarp = 11;
+    static constexpr int kSoftmaxRegs = 216;
+    static constexpr int kProducerRegs = 72;
+    static_assert(256 * kSoftmaxRegs + 128 * kProducerRegs <= 65536, "register file");
+
+    static constexpr int kBoxBytesQ = 128 * Base::kSwizzleElems * 2;   // Q box: 64 columns x 128 rows = 16 KiB
+    static constexpr int kQBytes = (kHeadDim / 64) * kBoxBytesQ;        // 32 KiB
+    static constexpr int kBoxBytesK = 64 * Base::kSwizzleElems * 2;    // K box of this CTA: 64 columns x 64 keys = 8 KiB
+    static constexpr int kSlotBytes = 16 * 1024;                        // half a K block (2 boxes) or half a V block (1 box of 128 keys)
+    static constexpr int kKStages = 4;
+    static constexpr int kVStages = 4;
+    static constexpr int kStages = kKStages + kVStages;
+    static constexpr int kNumBarriers = 1 /*q_full*/ + 2 * kStages + 2 /*s_full*/ + 2 /*s_free*/ + 2 /*p_full*/ + 2 /*o_done*/ + 4 /*m_pub*/;
+    static constexpr int kSmemTiles = kQBytes + kStages * kSlotBytes;
+    static constexpr int kTailBytes = 4096;  // barriers, TMEM slot, flags, running maxima, (m, l) exchange
+    static constexpr int kSmemSize = kSmemTiles + 1024 /*alignment slack*/ + kTailBytes;
+    static_assert(kNumBarriers * 8 + 64 + 128 * 4 + 4 * 128 * 4 <= kTailBytes, "tail layout");
+    static_assert(kSmemSize <= 227 * 1024, "exceeds the 227 KiB per-CTA limit");
+
+    // tensor memory: S of even blocks, S of odd blocks, P of even / odd blocks (16-bit pairs), O
+    static constexpr int kTmemCols = 512;
+    static constexpr int kTmemS0 = 0;
+    static constexpr int kTmemP0 = 256;
+    static constexpr int kTmemPCols = 64;
+    static constexpr int kTmemO = 384;
+    static_assert(kTmemO + kHeadDim <= kTmemCols, "TMEM budget");
+};

@@ -31,6 +31,7 @@
 
 #include "../../include/ring_attention_b200.h"
 #include "block_attention.cuh"
+#include "block_attention_pair.cuh"
 #include "kernel_traits.h"
 #include "lse_merge.cuh"
 #include "ring.h"
@@ -59,6 +60,9 @@ int fail(int code, const char* fmt, ...) {
     } while (0)
 
 std::atomic<int64_t> g_launches{0};
+#ifdef RING_TRACE
+long long* g_trace = nullptr;  // debug builds only: device buffer for clock stamps of one CTA
+#endif
 
 // ------------------------------------------------------------------------------------------ NCCL (loaded lazily)
 // The library is usable on one GPU without NCCL being present; multi-rank contexts load it on demand.
@@ -123,7 +127,7 @@ NcclApi& nccl() {
 struct DeviceState {
     int* d_status = nullptr;  // device status word written by kernels whose bounded waits ran out
     int sm_count = 0;
-    bool attr_set[2][2] = {{false, false}, {false, false}};  // [dim==128][bf16]
+    bool attr_set[8] = {};  // [pair form][dim == 128][bf16]: dynamic shared-memory attribute set
 };
 
 std::mutex g_dev_mutex;
@@ -169,7 +173,7 @@ int encode_fn(EncodeTiledFn* out) {
 // Out-of-range rows read as zero, which gives tail predication for free (the reference has none and
 // needs seqlen % 64 == 0, csrc/ring_attention.cu:131,143-145).
 int make_tensor_map(CUtensorMap* tm, const void* base, int batch, int heads, int rows, int dim, bool bf16,
-                    int64_t rows_total = 0) {
+                    int64_t rows_total = 0, int box_rows = 128) {
     if (rows_total <= 0) rows_total = rows;  // rows_total > rows: `base` points at a row range inside longer (b, h) slabs
     EncodeTiledFn enc = nullptr;
     int rc = encode_fn(&enc);
@@ -178,7 +182,7 @@ int make_tensor_map(CUtensorMap* tm, const void* base, int batch, int heads, int
                                 static_cast<cuuint64_t>(heads), static_cast<cuuint64_t>(batch)};
     const cuuint64_t strides[3] = {static_cast<cuuint64_t>(dim) * 2, static_cast<cuuint64_t>(rows_total) * dim * 2,
                                    static_cast<cuuint64_t>(heads) * rows_total * dim * 2};
-    const cuuint32_t box[4] = {64, 128, 1, 1};
+    const cuuint32_t box[4] = {64, static_cast<cuuint32_t>(box_rows), 1, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     CUresult r = enc(tm, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 4,
                      const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -241,28 +245,12 @@ struct BlockLaunch {
 // status word is allocated once per device); the no-allocation entry point passes the header of its fixed array.
 struct LaunchEnv {
     int* status;            // device status word the kernel reports a run-out wait in
-    bool (*attr_set)[2];    // [dim == 128][bf16]: dynamic shared-memory attribute already set on this device
+    bool* attr_set;         // [pair form][dim == 128][bf16]: dynamic shared-memory attribute already set on this device
     int sm_count;
 };
 
-template <class Traits>
-int launch_block_instance(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
-    auto kernel = &ring::ring_block_attention_kernel<Traits>;
-    {
-        std::lock_guard<std::mutex> lock(g_dev_mutex);
-        bool& attr = env.attr_set[Traits::kHeadDim == 128][Traits::kIsBf16];
-        if (!attr) {
-            RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
-            attr = true;
-        }
-    }
-    CUtensorMap tq, tk, tv;
-    int rc;
-    if ((rc = make_tensor_map(&tq, L.q, L.batch, L.heads, L.sq, L.dim, L.is_bf16, L.q_rows_total))) return rc;
-    if ((rc = make_tensor_map(&tk, L.k, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
-    if ((rc = make_tensor_map(&tv, L.v, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
+ring::BlockFwdArgs block_args(const BlockLaunch& L, const LaunchEnv& env) {
     const int64_t q_slab = L.q_rows_total > 0 ? L.q_rows_total : L.sq;
-
     ring::BlockFwdArgs a;
     a.o = L.o;
     a.lse = L.lse;
@@ -283,6 +271,56 @@ int launch_block_instance(const BlockLaunch& L, const LaunchEnv& env, cudaStream
     a.diag = static_cast<int>(diag);
     a.merge = L.merge ? 1 : 0;
     a.status = env.status;
+    a.rows_per_cta = 0;
+#ifdef RING_TRACE
+    a.trace = g_trace;
+#endif
+    return a;
+}
+
+// The CTA-pair form (head dimension 128): clusters of two CTAs, 128 Q rows each; K is fetched in boxes of 64 keys.
+template <class Traits>
+int launch_block_pair_instance(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
+    auto kernel = &ring::ring_block_attention_pair_kernel<Traits>;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        bool& attr = env.attr_set[4 + (Traits::kHeadDim == 128) * 2 + Traits::kIsBf16];
+        if (!attr) {
+            RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
+            attr = true;
+        }
+    }
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map(&tq, L.q, L.batch, L.heads, L.sq, L.dim, L.is_bf16, L.q_rows_total))) return rc;
+    if ((rc = make_tensor_map(&tk, L.k, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total, 64))) return rc;
+    if ((rc = make_tensor_map(&tv, L.v, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
+    ring::BlockFwdArgs a = block_args(L, env);
+    a.rows_per_cta = Traits::kBlockM;
+    dim3 grid(2 * ((L.sq + 255) / 256), L.batch * L.heads);  // whole pairs: a CTA whose rows lie past the end still loads its K/V halves
+    kernel<<<grid, dim3(Traits::kNThreads), Traits::kSmemSize, stream>>>(tq, tk, tv, a);
+    RING_CUDA(cudaGetLastError());
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return RING_OK;
+}
+
+template <class Traits>
+int launch_block_instance(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
+    auto kernel = &ring::ring_block_attention_kernel<Traits>;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        bool& attr = env.attr_set[(Traits::kHeadDim == 128) * 2 + Traits::kIsBf16];
+        if (!attr) {
+            RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
+            attr = true;
+        }
+    }
+    CUtensorMap tq, tk, tv;
+    int rc;
+    if ((rc = make_tensor_map(&tq, L.q, L.batch, L.heads, L.sq, L.dim, L.is_bf16, L.q_rows_total))) return rc;
+    if ((rc = make_tensor_map(&tk, L.k, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
+    if ((rc = make_tensor_map(&tv, L.v, L.batch, L.heads, L.sk, L.dim, L.is_bf16, L.k_rows_total))) return rc;
+    ring::BlockFwdArgs a = block_args(L, env);
 
     // Two Q tiles per CTA keep the tensor pipe busiest, but a grid that covers at most half of the SMs that way
     // (one head of a short shard, as in the reference's own driver) finishes sooner with one tile per CTA.
@@ -323,7 +361,19 @@ int validate_block(const BlockLaunch& L) {
 
 // Shape dispatch: the reference instantiates Ring_fwd_traits<64, 64, 64, 4, half> only
 // (csrc/ring_attention.cu:707-716); here <64|128, 256, 128, 12, half|bf16>.
+// RING_PAIR=1 in the environment: head dimension 128 runs the CTA-pair form (clusters of two CTAs, cta_group::2 MMAs,
+// two S buffers).  Default off: on the benchmark shape it measured 1.05-1.09 PFLOP/s against 1.15-1.23 for the one-CTA
+// form in the same runs.  Read at every launch so that tests can switch it.
+bool use_pair_form() {
+    const char* e = std::getenv("RING_PAIR");
+    return e && std::atoi(e) != 0;
+}
+
 int launch_block_env(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
+    if (L.dim == 128 && use_pair_form()) {
+        if (L.is_bf16) return launch_block_pair_instance<Ring_pair_traits<128, __nv_bfloat16>>(L, env, stream);
+        return launch_block_pair_instance<Ring_pair_traits<128, __half>>(L, env, stream);
+    }
     if (L.dim == 128) {
         if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(L, env, stream);
         return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __half>>(L, env, stream);
@@ -1404,7 +1454,7 @@ namespace {
 
 struct StaticSetup {
     float* base = nullptr;  // DEVICE address of g_static_scratch on this device (the symbol itself is a host-side stand-in)
-    bool attr_set[2][2] = {{false, false}, {false, false}};
+    bool attr_set[8] = {};
     int sm_count = 0;
 };
 std::mutex g_static_mutex;
@@ -1485,3 +1535,7 @@ extern "C" int ring_static_status(int* status_out, void* stream_) {
     RING_CUDA(cudaStreamSynchronize(stream));
     return RING_OK;
 }
+
+#ifdef RING_TRACE
+extern "C" int ring_debug_set_trace(long long* buf) { g_trace = buf; return 0; }
+#endif
