@@ -731,6 +731,39 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         raise SystemExit("bench.py: a parity check against the CPU oracle FAILED (see the parity objects of the line above)")
 
 
+def run_block_only(spec: str):
+    """--block-only B,H,Sq,Sk,D: a few launches of the block kernel alone on seeded inputs of that shape, one JSON line.
+    A small, bounded case of the same kernel for profiler captures (RING_PAIR=1 in the environment selects the
+    CTA-pair form)."""
+    import torch
+    import ringattention_b200 as ra
+    from ringattention_b200 import synthetic
+    Bc, Hc, Sq, Sk, Dc = (int(x) for x in spec.split(","))
+    torch.cuda.set_device(0)
+    q = torch.from_numpy(synthetic.make_shard("q", SEED, Bc, Hc, Dc, 0, Sq)).cuda()
+    k = torch.from_numpy(synthetic.make_shard("k", SEED, Bc, Hc, Dc, 0, Sk)).cuda()
+    v = torch.from_numpy(synthetic.make_shard("v", SEED, Bc, Hc, Dc, 0, Sk)).cuda()
+    o = torch.empty((Bc, Hc, Sq, Dc), device="cuda")
+    lse = torch.empty((Bc, Hc, Sq), device="cuda")
+    for _ in range(3):
+        ra.attention_block_fwd(q, k, v, o, lse)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 5
+    e0.record()
+    for _ in range(n):
+        ra.attention_block_fwd(q, k, v, o, lse)
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    assert ra.device_status() == 0
+    fl = 4.0 * Dc * Bc * Hc * Sq * Sk
+    print(json.dumps({"mode": "block-only", "shape": {"B": Bc, "H": Hc, "Sq": Sq, "Sk": Sk, "D": Dc}, "launches": 3 + n,
+                      "form": "cta-pair" if os.environ.get("RING_PAIR", "0") not in ("", "0") and Dc == 128 else "one-cta",
+                      "ms_per_launch": ms, "tflops": fl / (ms * 1e-3) / 1e12,
+                      "hbm_bytes_algorithmic": 2.0 * Bc * Hc * (Sq + 2 * Sk) * Dc + 4.0 * Bc * Hc * Sq * (Dc + 1)}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -744,7 +777,11 @@ def main():
     ap.add_argument("--merge-mode", type=int, default=None, choices=[0, 1], help="0 separate merge kernel, 1 fused epilogue")
     ap.add_argument("--configs", default="auto", help="auto: the BASELINE.json configurations of this GPU count; none; or a comma list")
     ap.add_argument("--nccl-ctas", default="4,16", help="CTA caps for the NCCL-transport pass at N > 1 (comma list), or none")
+    ap.add_argument("--block-only", default=None, metavar="B,H,Sq,Sk,D", help="only a few launches of the block kernel at this shape")
     args = ap.parse_args()
+    if args.block_only:
+        run_block_only(args.block_only)
+        return
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

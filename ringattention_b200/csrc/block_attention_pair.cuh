@@ -275,7 +275,6 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
             // S is in registers: the buffer is free for block j + 2
             tcgen05_fence_before_thread_sync();
             __syncwarp();
-            RING_PTRACE(quarter == 0 && lane == 0, j, 13);
             if (lane == 0) mbar_arrive_cluster(lead_s_free);
             RING_PTRACE(quarter == 0 && lane == 0, j, 5);
 
@@ -302,11 +301,12 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
             const float mx = fmaxf(fmax3(mxc[0], mxc[1], mxc[2]), fmax3(fmax3(mxc[3], mxc[4], mxc[5]), mxc[6], mxc[7]));
 
             // The maximum in use after block j - 1 (kept by the other warpgroup's thread of this row); adopt the block's
-            // own only when it beats that by more than 2^8.  The other thread hands it over only AFTER its
-            // exponentials (and this one does the same below): the two warps of a scheduler thereby take turns on the
-            // MUFU instead of running their exponentials at the same time and their load / max / pack phases at
-            // the same time, which leaves the MUFU idle for 40 % of the period (measured).
+            // own only when it beats that by more than 2^8, and hand the result on at once.  (Handing it on only after
+            // the exponentials, so that the two warps of a scheduler take strict turns on the MUFU, was measured: a
+            // warp's 128 exponentials take ~1500 clocks here with or without the other warp's, and the period did not
+            // improve.)
             float m_prev = -INFINITY;
+            RING_PTRACE(quarter == 0 && lane == 0, j, 13);
             if (j > 0) {
                 ok = mbar_wait(bar_m_pub(quarter), static_cast<uint32_t>((j - 1) & 1), abort_flag, a.status, kDevSoftmaxWaitM);
                 ok = __all_sync(0xffffffffu, ok);
@@ -316,6 +316,9 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
             RING_PTRACE(quarter == 0 && lane == 0, j, 6);
             float m_new = m_prev;
             if (mx > m_prev && (m_prev == -INFINITY || (mx - m_prev) * c > kRescaleThresholdLog2)) m_new = mx;
+            m_sh[row_local] = m_new;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_m_pub(quarter));
             const float alpha_o = (m_new != m_prev && m_prev != -INFINITY) ? ex2_approx((m_prev - m_new) * c) : 1.f;
             if (m_mine != m_new) {
                 l_mine = (m_mine == -INFINITY) ? 0.f : l_mine * ex2_approx((m_mine - m_new) * c);
@@ -338,9 +341,6 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                 fadd2(a2, a3, a2, a3, s[i + 2], s[i + 3]);
             }
             l_mine += (a0 + a1) + (a2 + a3);
-            m_sh[row_local] = m_new;  // hand the maximum (and the MUFU) to the thread of the next block
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_m_pub(quarter));
             RING_PTRACE(quarter == 0 && lane == 0, j, 7);
 
             // my P buffer was last read by P(j - 2) V: that product must be complete before it is overwritten
