@@ -180,7 +180,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
         } else if (warp == T::kQkWarp) {
             // =================================================================== UMMA issuer (leader): S(j) = Q K_j^T
             if (crank == 0 && lane == 0 && nblk > 0) {
-                const uint32_t peer_s_full[2] = {mapa_shared(bar_s_full(0), 1), mapa_shared(bar_s_full(1), 1)};
+                const uint32_t peer_s_full0 = mapa_shared(bar_s_full(0), 1), peer_s_full1 = mapa_shared(bar_s_full(1), 1);
                 bool ok = mbar_wait_cluster(bar_q_full, 0, abort_flag, a.status, kDevMmaWaitQ);
 #pragma unroll 1
                 for (int j = 0; j < nblk && ok; ++j) {
@@ -200,7 +200,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                                      umma_desc_kmajor_sw128(smem_slot(kslot) + off_k), kIdescQK, kk > 0 ? 1u : 0u);
                     }
                     umma_commit_pair(bar_s_full(par));
-                    umma_commit_pair(peer_s_full[par]);
+                    umma_commit_pair(par ? peer_s_full1 : peer_s_full0);
                     umma_commit_pair(bar_kv_empty(kslot));
                     umma_commit_pair(mapa_shared(bar_kv_empty(kslot), 1));
                     RING_PTRACE(true, j, 1);
@@ -210,7 +210,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
         } else if (warp == T::kPvWarp) {
             // =================================================================== UMMA issuer (leader): O += P(j) V_j
             if (crank == 0 && lane == 0 && nblk > 0) {
-                const uint32_t peer_o_done[2] = {mapa_shared(bar_o_done(0), 1), mapa_shared(bar_o_done(1), 1)};
+                const uint32_t peer_o_done0 = mapa_shared(bar_o_done(0), 1), peer_o_done1 = mapa_shared(bar_o_done(1), 1);
                 bool ok = true;
 #pragma unroll 1
                 for (int j = 0; j < nblk && ok; ++j) {
@@ -230,7 +230,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                                      (j > 0 || kk > 0) ? 1u : 0u);
                     }
                     umma_commit_pair(bar_o_done(buf));
-                    umma_commit_pair(peer_o_done[buf]);
+                    umma_commit_pair(buf ? peer_o_done1 : peer_o_done0);
                     umma_commit_pair(bar_kv_empty(vslot));
                     umma_commit_pair(mapa_shared(bar_kv_empty(vslot), 1));
                     RING_PTRACE(true, j, 3);
