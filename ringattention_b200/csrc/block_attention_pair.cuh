@@ -12,8 +12,9 @@
 //   * with one Q tile per CTA the tensor memory holds TWO S buffers (even and odd K/V blocks), two P buffers and O:
 //     S(j + 1) is computed while block j is in its softmax, so the tensor pipe never waits for an S buffer to be
 //     read out (the one-buffer form spends about a quarter of its time in that hand-off);
-//   * two softmax warpgroups share the 128 rows: warpgroup 0 takes the even K/V blocks, warpgroup 1 the odd ones,
-//     one thread per row in each.  The running maximum of a row is a value in shared memory that the two
+//   * two groups of softmax warps share the 128 rows: one takes the even K/V blocks, the other the odd ones, with
+//     one thread per row in each (kHalves = 1) or two threads per row that split the block's 128 columns and exchange
+//     the maxima of their halves through shared memory (kHalves = 2: four softmax warps per scheduler).  The running maximum of a row is a value in shared memory that the two
 //     threads of the row hand to each other block by block (a new maximum is adopted only when it beats the one in
 //     use by more than 2^8, so it rarely changes and O is rarely rescaled); each thread keeps the sum of its own
 //     blocks and the two are combined at the end;
@@ -43,6 +44,8 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
     using namespace ptx;
     constexpr int D = T::kHeadDim;
     constexpr int kKS = T::kKStages, kVS = T::kVStages, kStages = T::kStages;
+    constexpr int kH = T::kHalves;       // threads per Q row and block parity
+    constexpr int kC = 128 / kH;         // columns of a block each of them handles
     constexpr uint32_t kIdescQK = umma_idesc_f16(256, T::kBlockN, false, false, T::kIsBf16);
     constexpr uint32_t kIdescPV = umma_idesc_f16(256, D, false, true, T::kIsBf16);
 
@@ -55,8 +58,9 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + T::kNumBarriers);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* prior_error = reinterpret_cast<volatile int*>(tmem_slot + 2);
-    volatile float* m_sh = reinterpret_cast<volatile float*>(tail + 512);      // [128] maximum in use, per row
-    volatile float* xl = reinterpret_cast<volatile float*>(tail + 1024);       // [2][128][2]: (maximum, sum) of each warpgroup
+    volatile float* m_sh = reinterpret_cast<volatile float*>(tail + T::kTailMaxima);   // [2][128] maximum in use after block j, at [j & 1]
+    volatile float* hmax_sh = reinterpret_cast<volatile float*>(tail + T::kTailHalfMax);  // [parity][half][n & 1][128] block maximum of a column half
+    volatile float* xl = reinterpret_cast<volatile float*>(tail + T::kTailSums);        // [parity * kHalves + half][128][2]: (maximum, sum) of each thread of a row
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t bar_q_full = bar0;
@@ -67,6 +71,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
     auto bar_p_full = [&](int b) { return bar0 + 8u * (5 + 2 * kStages + b); };
     auto bar_o_done = [&](int b) { return bar0 + 8u * (7 + 2 * kStages + b); };
     auto bar_m_pub = [&](int q) { return bar0 + 8u * (9 + 2 * kStages + q); };
+    auto bar_half_max = [&](int g, int q) { return bar0 + 8u * (13 + 2 * kStages + g * 4 + q); };
     const uint32_t smem_q = base;
     auto smem_slot = [&](int s) { return base + static_cast<uint32_t>(T::kQBytes + s * T::kSlotBytes); };
 
@@ -91,11 +96,12 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_s_full(b), 1);
-            mbar_init(bar_s_free(b), 8);  // four softmax warps in each CTA
-            mbar_init(bar_p_full(b), 8);
+            mbar_init(bar_s_free(b), 8 * kH);  // the parity's softmax warps of both CTAs
+            mbar_init(bar_p_full(b), 8 * kH);
             mbar_init(bar_o_done(b), 1);
+            for (int q = 0; q < 4; ++q) mbar_init(bar_half_max(b, q), 2);
         }
-        for (int q = 0; q < 4; ++q) mbar_init(bar_m_pub(q), 1);
+        for (int q = 0; q < 4; ++q) mbar_init(bar_m_pub(q), kH);
         fence_mbar_init();
     }
     if (warp == T::kLoadWarp && lane == 0) {
@@ -133,7 +139,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
     }
 
     if (warp >= T::kSoftmaxWarps) {
-        // ############################################################## producer warpgroup (warps 8..11)
+        // ############################################################## producer warpgroup (the last four warps)
         setmaxnreg_dec<T::kProducerRegs>();
         if (warp == T::kLoadWarp) {
             // =================================================================== TMA producer of Q and K (both CTAs)
@@ -239,84 +245,95 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
             __syncwarp();
         }
     } else {
-        // ############################################################## softmax warpgroups (warps 0..7)
+        // ############################################################## softmax warpgroups
         setmaxnreg_inc<T::kSoftmaxRegs>();
-        const int g = warp >> 2;  // 0: even K/V blocks, 1: odd ones
-        const int quarter = warp & 3;
-        const int row_local = quarter * 32 + lane;  // row of the CTA's Q tile == TMEM lane
+        const int quarter = warp & 3;                       // TMEM lane quarter this warp may touch
+        const int hf = kH == 2 ? ((warp >> 2) & 1) : 0;      // column half of the block (two threads per row)
+        const int g = warp >> (kH == 2 ? 3 : 2);             // 0: even K/V blocks, 1: odd ones
+        const int row_local = quarter * 32 + lane;          // row of the CTA's Q tile == TMEM lane
         const int row = r0 + row_local;
         const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-        const uint32_t t_s = tmem_base + lane_addr + T::kTmemS0 + g * T::kBlockN;
-        const uint32_t t_p = tmem_base + lane_addr + T::kTmemP0 + g * T::kTmemPCols;
+        const uint32_t t_s = tmem_base + lane_addr + T::kTmemS0 + g * T::kBlockN + hf * kC;
+        const uint32_t t_p = tmem_base + lane_addr + T::kTmemP0 + g * T::kTmemPCols + hf * (kC / 2);
         const uint32_t t_o = tmem_base + lane_addr + T::kTmemO;
         const uint32_t lead_s_free = mapa_shared(bar_s_free(g), 0);
         const uint32_t lead_p_full = mapa_shared(bar_p_full(g), 0);
         const float c = a.scale_log2;
 
         float m_mine = -INFINITY;  // maximum my sum is taken against (raw score)
-        float l_mine = 0.f;        // sum of exp2((s - m_mine) c) over my blocks, from unrounded fp32 p
+        float l_mine = 0.f;        // sum of exp2((s - m_mine) c) over my blocks and columns, from unrounded fp32 p
         bool ok = true;
 
 #pragma unroll 1
         for (int j = g; j < nblk; j += 2) {
             const int n = j >> 1;  // my n-th block
-            uint32_t sr[128];
+            uint32_t sr[kC];
             float* s = reinterpret_cast<float*>(sr);
             ok = mbar_wait_cluster(bar_s_full(g), static_cast<uint32_t>(n & 1), abort_flag, a.status, kDevSoftmaxWaitS);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
-            RING_PTRACE(quarter == 0 && lane == 0, j, 4);
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 4);
             tcgen05_fence_after_thread_sync();
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < kC / 32; ++i)
                 tmem_ld_x32(t_s + 32 * i, *reinterpret_cast<uint32_t(*)[32]>(&sr[32 * i]));
             tmem_wait_ld();
-            RING_PTRACE(quarter == 0 && lane == 0, j, 12);
             // S is in registers: the buffer is free for block j + 2
             tcgen05_fence_before_thread_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_s_free);
-            RING_PTRACE(quarter == 0 && lane == 0, j, 5);
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 5);
 
             // masking: only blocks that straddle the causal diagonal or the end of the shard
             const int col0 = j * T::kBlockN;
             int limit = a.sk - col0;                                  // valid columns of this block
             if (a.causal) limit = min(limit, row + a.diag - col0 + 1);  // visible columns of this row
+            limit -= hf * kC;                                          // ... counted from this thread's first column
             const bool masked_block = (a.sk - col0 < T::kBlockN) || (a.causal && (r0 + a.diag - col0 + 1) < T::kBlockN);
             if (masked_block) {
 #pragma unroll
-                for (int i = 0; i < 128; ++i)
+                for (int i = 0; i < kC; ++i)
                     if (i >= limit) s[i] = -INFINITY;
             }
 
-            // row maximum of the block: eight independent chains, then a tree
+            // row maximum of the block (of this thread's columns): eight independent chains, then a tree
             float mxc[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) mxc[u] = fmaxf(s[2 * u], s[2 * u + 1]);
 #pragma unroll
-            for (int i = 16; i < 128; i += 16) {
+            for (int i = 16; i < kC; i += 16) {
 #pragma unroll
                 for (int u = 0; u < 8; ++u) mxc[u] = fmax3(mxc[u], s[i + 2 * u], s[i + 2 * u + 1]);
             }
-            const float mx = fmaxf(fmax3(mxc[0], mxc[1], mxc[2]), fmax3(fmax3(mxc[3], mxc[4], mxc[5]), mxc[6], mxc[7]));
+            float mx = fmaxf(fmax3(mxc[0], mxc[1], mxc[2]), fmax3(fmax3(mxc[3], mxc[4], mxc[5]), mxc[6], mxc[7]));
+            if (kH == 2) {
+                // the two threads of the row exchange the maxima of their halves (slots alternate with n so that a
+                // value is never overwritten before the partner has read it)
+                hmax_sh[((g * 2 + hf) * 2 + (n & 1)) * 128 + row_local] = mx;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_half_max(g, quarter));
+                ok = mbar_wait(bar_half_max(g, quarter), static_cast<uint32_t>(n & 1), abort_flag, a.status, kDevSoftmaxWaitM);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                mx = fmaxf(mx, hmax_sh[((g * 2 + (hf ^ 1)) * 2 + (n & 1)) * 128 + row_local]);
+            }
 
-            // The maximum in use after block j - 1 (kept by the other warpgroup's thread of this row); adopt the block's
-            // own only when it beats that by more than 2^8, and hand the result on at once.  (Handing it on only after
-            // the exponentials, so that the two warps of a scheduler take strict turns on the MUFU, was measured: a
-            // warp's 128 exponentials take ~1500 clocks here with or without the other warp's, and the period did not
-            // improve.)
+            // The maximum in use after block j - 1 (kept by the threads of the other block parity); adopt the block's
+            // own only when it beats that by more than 2^8, and hand the result on at once.  Every thread of the row
+            // computes the same value; the first half stores it, all of them arrive (so that it is overwritten, two
+            // blocks later, only after every reader of it has passed).
             float m_prev = -INFINITY;
-            RING_PTRACE(quarter == 0 && lane == 0, j, 13);
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 13);
             if (j > 0) {
                 ok = mbar_wait(bar_m_pub(quarter), static_cast<uint32_t>((j - 1) & 1), abort_flag, a.status, kDevSoftmaxWaitM);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
-                m_prev = m_sh[row_local];
+                m_prev = m_sh[((j - 1) & 1) * 128 + row_local];
             }
-            RING_PTRACE(quarter == 0 && lane == 0, j, 6);
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 6);
             float m_new = m_prev;
             if (mx > m_prev && (m_prev == -INFINITY || (mx - m_prev) * c > kRescaleThresholdLog2)) m_new = mx;
-            m_sh[row_local] = m_new;
+            if (hf == 0) m_sh[(j & 1) * 128 + row_local] = m_new;
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_m_pub(quarter));
             const float alpha_o = (m_new != m_prev && m_prev != -INFINITY) ? ex2_approx((m_prev - m_new) * c) : 1.f;
@@ -329,7 +346,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
             const float nms = (m_new == -INFINITY) ? 0.f : -m_new * c;
             float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
-            for (int i = 0; i < 128; i += 4) {
+            for (int i = 0; i < kC; i += 4) {
 #pragma unroll
                 for (int u = 0; u < 4; u += 2) {
                     float x0, x1;
@@ -341,7 +358,7 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                 fadd2(a2, a3, a2, a3, s[i + 2], s[i + 3]);
             }
             l_mine += (a0 + a1) + (a2 + a3);
-            RING_PTRACE(quarter == 0 && lane == 0, j, 7);
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 7);
 
             // my P buffer was last read by P(j - 2) V: that product must be complete before it is overwritten
             if (n > 0) {
@@ -349,8 +366,10 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
             }
-            // O is rescaled only when some row of the warp adopted a new maximum; P(j - 1) V (the other warpgroup's
-            // block) must be complete first, and P(j) V cannot start before this warp has written P(j)
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 8);
+            // O is rescaled only when some row of the warp adopted a new maximum (the threads of a row agree, and share
+            // the columns of O); P(j - 1) V (the other parity's block) must be complete first, and P(j) V cannot start
+            // before this warp has written P(j)
             if (__any_sync(0xffffffffu, alpha_o != 1.f)) {
                 const uint32_t par = static_cast<uint32_t>((g == 0 ? n - 1 : n) & 1);
                 ok = mbar_wait_cluster(bar_o_done(g ^ 1), par, abort_flag, a.status, kDevSoftmaxWaitO);
@@ -358,46 +377,44 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                 if (!ok) break;
                 tcgen05_fence_after_thread_sync();
 #pragma unroll
-                for (int i = 0; i < D / 32; ++i) {
-                    uint32_t orr[32];
-                    tmem_ld_x32(t_o + 32 * i, orr);
+                for (int i = 0; i < D / kH / 16; ++i) {  // 16 columns at a time: S is still live in registers
+                    uint32_t orr[16];
+                    tmem_ld_x16(t_o + hf * (D / kH) + 16 * i, orr);
                     tmem_wait_ld();
 #pragma unroll
-                    for (int x = 0; x < 32; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha_o);
-                    tmem_st_x32(t_o + 32 * i, orr);
+                    for (int x = 0; x < 16; ++x) orr[x] = __float_as_uint(__uint_as_float(orr[x]) * alpha_o);
+                    tmem_st_x16(t_o + hf * (D / kH) + 16 * i, orr);
                 }
             }
 
-            // P(j): 128 probabilities -> 64 columns of 16-bit pairs
-            RING_PTRACE(quarter == 0 && lane == 0, j, 8);
+            // P(j): this thread's probabilities -> columns of 16-bit pairs
             tcgen05_fence_after_thread_sync();
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-                uint32_t pk[32];
+            for (int i = 0; i < kC / 32; ++i) {
+                uint32_t pk[16];
 #pragma unroll
-                for (int x = 0; x < 32; ++x)
-                    pk[x] = T::kIsBf16 ? pack_bf16x2(s[64 * i + 2 * x], s[64 * i + 2 * x + 1])
-                                       : pack_f16x2(s[64 * i + 2 * x], s[64 * i + 2 * x + 1]);
-                tmem_st_x32(t_p + 32 * i, pk);
+                for (int x = 0; x < 16; ++x)
+                    pk[x] = T::kIsBf16 ? pack_bf16x2(s[32 * i + 2 * x], s[32 * i + 2 * x + 1])
+                                       : pack_f16x2(s[32 * i + 2 * x], s[32 * i + 2 * x + 1]);
+                tmem_st_x16(t_p + 16 * i, pk);
             }
-            RING_PTRACE(quarter == 0 && lane == 0, j, 14);
             tmem_wait_st();
-            RING_PTRACE(quarter == 0 && lane == 0, j, 15);
             tcgen05_fence_before_thread_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(lead_p_full);
-            RING_PTRACE(quarter == 0 && lane == 0, j, 9);
+            RING_PTRACE(warp == 4 * kH * g && lane == 0, j, 9);
         }
 
-        // ---- the two threads of a row meet: (maximum, sum) of each, and the earlier partial's LSE -----------
+        // ---- the threads of a row meet: (maximum, sum) of each, and the earlier partial's LSE -----------
         const bool row_ok = row < a.sq;
         float* lse_ptr = a.lse + b * a.lse_batch_stride + h * a.lse_head_stride + row;
-        const float lse_old = (a.merge && row_ok) ? *lse_ptr : -INFINITY;  // read before warpgroup 0 overwrites it
-        xl[(g * 128 + row_local) * 2 + 0] = m_mine;
-        xl[(g * 128 + row_local) * 2 + 1] = l_mine;
-        asm volatile("bar.sync 1, 256;" ::: "memory");  // all eight softmax warps, on every path
+        const float lse_old = (a.merge && row_ok) ? *lse_ptr : -INFINITY;  // read before it is overwritten below
+        xl[((g * kH + hf) * 128 + row_local) * 2 + 0] = m_mine;
+        xl[((g * kH + hf) * 128 + row_local) * 2 + 1] = l_mine;
+        asm volatile("bar.sync 1, %0;" ::"n"(T::kSoftmaxWarps * 32) : "memory");  // all softmax warps, on every path
 
-        // ---- epilogue: O / l, LSE, optional fold into an earlier partial; warpgroup g writes columns [64 g, 64 g + 64)
+        // ---- epilogue: O / l, LSE, optional fold into an earlier partial; every softmax warp writes its 32 rows of
+        // D / (2 kHalves) columns
         if (ok && nblk > 0) {
             const int last = nblk - 1;
             ok = mbar_wait_cluster(bar_o_done(last & 1), static_cast<uint32_t>((last >> 1) & 1), abort_flag, a.status, kDevSoftmaxWaitO);
@@ -405,10 +422,10 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
             if (ok) tcgen05_fence_after_thread_sync();
         }
         if (ok) {
-            const float m_f = nblk > 0 ? m_sh[row_local] : -INFINITY;  // published by the warpgroup of the last block
+            const float m_f = nblk > 0 ? m_sh[((nblk - 1) & 1) * 128 + row_local] : -INFINITY;  // stored by the threads of the last block
             float l_run = 0.f;
 #pragma unroll
-            for (int gg = 0; gg < 2; ++gg) {
+            for (int gg = 0; gg < 2 * kH; ++gg) {
                 const float mg = xl[(gg * 128 + row_local) * 2 + 0];
                 const float lg = xl[(gg * 128 + row_local) * 2 + 1];
                 if (mg != -INFINITY) l_run += lg * ex2_approx((mg - m_f) * c);
@@ -431,16 +448,16 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                     lse_new = mx + logf(tot);
                 }
             }
-            // O goes out through shared memory so that every store instruction writes whole row pieces: warpgroup 0
-            // stages in the Q tile, warpgroup 1 in the first two K slots (every MMA that read them has completed),
-            // 16-byte chunks XOR-swizzled by the row.
-            constexpr int kHalfCols = D / 2;
-            constexpr int kChunks = kHalfCols / 4;
-            constexpr int kRowsPerInst = 32 / kChunks;
-            const uint32_t stage = (g == 0 ? smem_q : smem_slot(0)) + static_cast<uint32_t>(quarter) * (32 * kHalfCols * 4);
+            // O goes out through shared memory so that every store instruction writes whole row pieces: the first half
+            // of the softmax warps stages in the Q tile, the second half in the first two K slots (every MMA that read
+            // them has completed), 16-byte chunks XOR-swizzled by the row.
+            constexpr int kCols = D / (2 * kH);           // columns this warp writes
+            constexpr int kChunks = kCols / 4;            // 16-byte chunks per staged row
+            constexpr int kRowsPerInst = 32 / kChunks;    // rows one coalesced instruction covers
+            const int pass = g * kH + hf;                 // which group of kCols columns
+            const uint32_t stage = (warp < 4 * kH ? smem_q : smem_slot(0)) + static_cast<uint32_t>(warp % (4 * kH)) * (32 * kCols * 4);
             const int row_base = r0 + quarter * 32;
             float* o_base = a.o + b * a.o_batch_stride + h * a.o_head_stride;
-            const int pass = g;
             float4 old[32 / kRowsPerInst];
             if (a.merge) {
 #pragma unroll
@@ -449,14 +466,14 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                     old[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
                     if (row_base + rl < a.sq)
                         old[rr] = *(reinterpret_cast<const float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride +
-                                                                    pass * kHalfCols) + lane % kChunks);
+                                                                    pass * kCols) + lane % kChunks);
                 }
             }
 #pragma unroll
-            for (int i = 0; i < kHalfCols / 32; ++i) {
+            for (int i = 0; i < kCols / 32; ++i) {
                 uint32_t orr[32];
                 if (nblk > 0) {
-                    tmem_ld_x32(t_o + pass * kHalfCols + 32 * i, orr);
+                    tmem_ld_x32(t_o + pass * kCols + 32 * i, orr);
                     tmem_wait_ld();
                 } else {
 #pragma unroll
@@ -486,9 +503,9 @@ ring_block_attention_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const
                     val.w = fmaf(old[rr].w, wo, val.w);
                 }
                 if (row_base + rl < a.sq)
-                    *(reinterpret_cast<float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride + pass * kHalfCols) + ch) = val;
+                    *(reinterpret_cast<float4*>(o_base + static_cast<int64_t>(row_base + rl) * a.o_row_stride + pass * kCols) + ch) = val;
             }
-            if (g == 0 && row_ok) *lse_ptr = lse_new;
+            if (g == 0 && hf == 0 && row_ok) *lse_ptr = lse_new;
         }
     }
 

@@ -89,32 +89,44 @@ struct Ring_fwd_traits : public Base
 // K/V stream of a 256-row CTA, which leaves shared memory for deep K/V rings and, with one Q tile instead of two,
 // tensor memory for TWO S buffers: S of block j + 1 is computed while block j is still in its softmax.
 // Same constant names as Ring_fwd_traits where they mean the same thing.
-template <int kHeadDim_, typename elem_type = __half, typename Base = Ring_kernel_traits<kHeadDim_, 128, 128, 12, elem_type>>
+template <int kHeadDim_, typename elem_type = __half, int kHalves_ = 1,
+          typename Base = Ring_kernel_traits<kHeadDim_, 128, 128, 8 * kHalves_ + 4, elem_type>>
 struct Ring_pair_traits : public Base
 {
     using Element = typename Base::Element;
     using ElementAccum = typename Base::ElementAccum;
     using index_t = typename Base::index_t;
 
-    static constexpr int kNWarps = 12;
+    // kHalves = 1: one softmax thread per Q row and block parity (8 softmax warps, two per scheduler);
+    // kHalves = 2: two threads per row, 64 of the block's 128 columns each (16 softmax warps, four per scheduler,
+    // to overlap the latencies of the load / max / pack phases and of the barrier waits).
+    static constexpr int kHalves = kHalves_;
+    static_assert(kHalves == 1 || kHalves == 2, "one or two threads per row");
+    static constexpr int kSoftmaxWarps = 8 * kHalves;
+    static constexpr int kNWarps = kSoftmaxWarps + 4;
     static constexpr int kNThreads = kNWarps * 32;
     static constexpr int kBlockM = 128;        // Q rows per CTA (256 per pair)
     static constexpr int kBlockN = 128;        // K/V rows per block (64 of them, or 64 value columns, per CTA)
     static constexpr int kHeadDim = kHeadDim_;
     static_assert(kHeadDim == 128, "the pair form is instantiated for head dimension 128");
 
-    // warps 0-3 / 4-7: softmax warpgroups of the even / odd K/V blocks (one thread per Q row in each);
-    // warp 8: TMEM allocation, and in the leader CTA the issuer of S = Q K^T; warp 9 (leader): issuer of O += P V;
-    // warp 10: TMA loads of V; warp 11: TMA loads of Q and K (K slots are released early, V slots late: one thread
-    // for both would hold the K loads back behind a V slot that is still being read).
-    static constexpr int kSoftmaxWarps = 8;
-    static constexpr int kQkWarp = 8;
-    static constexpr int kPvWarp = 9;
-    static constexpr int kLoadWarpV = 10;
-    static constexpr int kLoadWarp = 11;
-    static constexpr int kSoftmaxRegs = 216;
-    static constexpr int kProducerRegs = 72;
-    static_assert(256 * kSoftmaxRegs + 128 * kProducerRegs <= 65536, "register file");
+    // softmax warp w: TMEM lane quarter w & 3, column half (w >> 2) & (kHalves - 1), block parity w >> (1 + kHalves);
+    // then one producer warpgroup: TMEM allocation and (leader CTA) issuer of S = Q K^T; (leader) issuer of O += P V;
+    // TMA loads of V; TMA loads of Q and K (K slots are released early, V slots late: one thread for both would
+    // hold the K loads back behind a V slot that is still being read).
+    static constexpr int kQkWarp = kSoftmaxWarps;
+    static constexpr int kPvWarp = kSoftmaxWarps + 1;
+    static constexpr int kLoadWarpV = kSoftmaxWarps + 2;
+    static constexpr int kLoadWarp = kSoftmaxWarps + 3;
+    static constexpr int kSoftmaxRegs = kHalves == 1 ? 216 : 112;
+    static constexpr int kProducerRegs = kHalves == 1 ? 72 : 32;
+    static_assert(kSoftmaxWarps * 32 * kSoftmaxRegs + 128 * kProducerRegs <= 65536, "register file");
+    // setmaxnreg.inc blocks until the CTA's own pool holds the registers, and that pool is only what setmaxnreg.dec
+    // gave back (registers of the SM that the launch never assigned to the CTA do not count: a form that relied on
+    // them never came back from the first setmaxnreg.inc).  Registers per thread at launch: 65536 / threads, in eights.
+    static constexpr int kLaunchRegs = (65536 / kNThreads) / 8 * 8;
+    static_assert((kLaunchRegs - kProducerRegs) * 128 >= (kSoftmaxRegs - kLaunchRegs) * kSoftmaxWarps * 32,
+                  "the producer warpgroup must give back at least what the softmax warps take");
 
     static constexpr int kBoxBytesQ = 128 * Base::kSwizzleElems * 2;   // Q box: 64 columns x 128 rows = 16 KiB
     static constexpr int kQBytes = (kHeadDim / 64) * kBoxBytesQ;        // 32 KiB
@@ -123,11 +135,13 @@ struct Ring_pair_traits : public Base
     static constexpr int kKStages = 4;
     static constexpr int kVStages = 4;
     static constexpr int kStages = kKStages + kVStages;
-    static constexpr int kNumBarriers = 1 /*q_full*/ + 2 * kStages + 2 /*s_full*/ + 2 /*s_free*/ + 2 /*p_full*/ + 2 /*o_done*/ + 4 /*m_pub*/;
+    static constexpr int kNumBarriers = 1 /*q_full*/ + 2 * kStages + 2 /*s_full*/ + 2 /*s_free*/ + 2 /*p_full*/ + 2 /*o_done*/ +
+                                        4 /*m_pub*/ + 8 /*half_max*/;
     static constexpr int kSmemTiles = kQBytes + kStages * kSlotBytes;
-    static constexpr int kTailBytes = 4096;  // barriers, TMEM slot, flags, running maxima, (m, l) exchange
+    // tail: barriers, TMEM slot, flags | running maxima [2][128] | block maxima of the halves [2][2][2][128] | (m, l) [4][128][2]
+    static constexpr int kTailMaxima = 512, kTailHalfMax = 1536, kTailSums = 5632, kTailBytes = 10240;
     static constexpr int kSmemSize = kSmemTiles + 1024 /*alignment slack*/ + kTailBytes;
-    static_assert(kNumBarriers * 8 + 64 + 128 * 4 + 4 * 128 * 4 <= kTailBytes, "tail layout");
+    static_assert(kNumBarriers * 8 + 64 <= kTailMaxima && kTailSums + 4 * 128 * 2 * 4 <= kTailBytes, "tail layout");
     static_assert(kSmemSize <= 227 * 1024, "exceeds the 227 KiB per-CTA limit");
 
     // tensor memory: S of even blocks, S of odd blocks, P of even / odd blocks (16-bit pairs), O

@@ -127,7 +127,7 @@ NcclApi& nccl() {
 struct DeviceState {
     int* d_status = nullptr;  // device status word written by kernels whose bounded waits ran out
     int sm_count = 0;
-    bool attr_set[8] = {};  // [pair form][dim == 128][bf16]: dynamic shared-memory attribute set
+    bool attr_set[12] = {};  // [one-CTA | pair | pair with two threads per row][dim == 128][bf16]: shared-memory attribute set
 };
 
 std::mutex g_dev_mutex;
@@ -284,7 +284,7 @@ int launch_block_pair_instance(const BlockLaunch& L, const LaunchEnv& env, cudaS
     auto kernel = &ring::ring_block_attention_pair_kernel<Traits>;
     {
         std::lock_guard<std::mutex> lock(g_dev_mutex);
-        bool& attr = env.attr_set[4 + (Traits::kHeadDim == 128) * 2 + Traits::kIsBf16];
+        bool& attr = env.attr_set[4 * Traits::kHalves + (Traits::kHeadDim == 128) * 2 + Traits::kIsBf16];
         if (!attr) {
             RING_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Traits::kSmemSize));
             attr = true;
@@ -361,18 +361,24 @@ int validate_block(const BlockLaunch& L) {
 
 // Shape dispatch: the reference instantiates Ring_fwd_traits<64, 64, 64, 4, half> only
 // (csrc/ring_attention.cu:707-716); here <64|128, 256, 128, 12, half|bf16>.
-// RING_PAIR=1 in the environment: head dimension 128 runs the CTA-pair form (clusters of two CTAs, cta_group::2 MMAs,
-// two S buffers).  Default off: on the benchmark shape it measured 1.05-1.09 PFLOP/s against 1.15-1.23 for the one-CTA
-// form in the same runs.  Read at every launch so that tests can switch it.
-bool use_pair_form() {
+// RING_PAIR=1 or 2 in the environment: head dimension 128 runs the CTA-pair form (clusters of two CTAs, cta_group::2
+// MMAs, two S buffers) with one or two softmax threads per Q row.  Default 0: the one-CTA form.  Read at every launch
+// so that tests can switch it.
+int pair_form() {
     const char* e = std::getenv("RING_PAIR");
-    return e && std::atoi(e) != 0;
+    const int v = e ? std::atoi(e) : 0;
+    return (v == 1 || v == 2) ? v : 0;
 }
 
 int launch_block_env(const BlockLaunch& L, const LaunchEnv& env, cudaStream_t stream) {
-    if (L.dim == 128 && use_pair_form()) {
-        if (L.is_bf16) return launch_block_pair_instance<Ring_pair_traits<128, __nv_bfloat16>>(L, env, stream);
-        return launch_block_pair_instance<Ring_pair_traits<128, __half>>(L, env, stream);
+    const int pair = L.dim == 128 ? pair_form() : 0;
+    if (pair == 2) {
+        if (L.is_bf16) return launch_block_pair_instance<Ring_pair_traits<128, __nv_bfloat16, 2>>(L, env, stream);
+        return launch_block_pair_instance<Ring_pair_traits<128, __half, 2>>(L, env, stream);
+    }
+    if (pair == 1) {
+        if (L.is_bf16) return launch_block_pair_instance<Ring_pair_traits<128, __nv_bfloat16, 1>>(L, env, stream);
+        return launch_block_pair_instance<Ring_pair_traits<128, __half, 1>>(L, env, stream);
     }
     if (L.dim == 128) {
         if (L.is_bf16) return launch_block_instance<Ring_fwd_traits<128, 256, 128, 12, __nv_bfloat16>>(L, env, stream);
@@ -1454,7 +1460,7 @@ namespace {
 
 struct StaticSetup {
     float* base = nullptr;  // DEVICE address of g_static_scratch on this device (the symbol itself is a host-side stand-in)
-    bool attr_set[8] = {};
+    bool attr_set[12] = {};
     int sm_count = 0;
 };
 std::mutex g_static_mutex;

@@ -1,5 +1,5 @@
-"""The CTA-pair form of the block kernel (RING_PAIR=1: clusters of two CTAs, tcgen05 cta_group::2, head dimension 128)
-against the CPU oracle, through the same C-ABI entry points as the one-CTA form, and against that form itself."""
+"""The CTA-pair forms of the block kernel (RING_PAIR=1 / 2: clusters of two CTAs, tcgen05 cta_group::2, head dimension
+128, one or two softmax threads per Q row) against the CPU oracle, through the same C-ABI entry points as the one-CTA form."""
 import numpy as np
 import pytest
 
@@ -10,9 +10,9 @@ from tests.gpu_util import assert_parity, to_dev
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True)
-def pair_form(monkeypatch):
-    monkeypatch.setenv("RING_PAIR", "1")
+@pytest.fixture(autouse=True, params=["1", "2"], ids=["one-thread-per-row", "two-threads-per-row"])
+def pair_form(request, monkeypatch):
+    monkeypatch.setenv("RING_PAIR", request.param)
 
 
 def _block(q, k, v, scale, **kw):
