@@ -408,6 +408,10 @@ def run_config(rig: Rig, ra, ctx, name: str, cfg: dict) -> dict:
         pairs_mine = float(Sl) * S
     my_tflops_busy = 4.0 * Dc * Bc * Hc * pairs_mine / max(busy_ms * 1e-3, 1e-9) / 1e12
     busy = rig.reduce([my_tflops_busy], "min") + rig.reduce([my_tflops_busy], "max")
+    # The forward lasts as long as its busiest rank (under a contiguous causal mask the last one): what the exchange
+    # costs is the part of the forward that rank did not spend in its kernels.  The max over ranks of a rank's own
+    # exposed fraction (exposed_frac below) also counts lightly loaded ranks waiting for work that delays nobody.
+    busy_ms_max = rig.reduce([busy_ms], "max")[0]
     par = check_parity(rig, cfg, seed, q, out, lse, segs, cfg["heads"], cfg["rows"])
     ctx.set_option(ra.RING_OPT_CAUSAL_ZIGZAG, 0)
     res = {"shape": {k2: cfg[k2] for k2 in ("B", "H", "S", "D", "causal", "gain")}, "world": rig.world,
@@ -416,6 +420,8 @@ def run_config(rig: Rig, ra, ctx, name: str, cfg: dict) -> dict:
            "forwards_timed": reps, "ms_per_forward": ms_fwd,
            "tflops_per_gpu": config_flops(cfg) / (ms_fwd * 1e-3) / 1e12 / rig.world,
            "busy_tflops_per_rank_min_max": busy,
+           "busiest_rank_kernel_ms": busy_ms_max,
+           "exposed_frac_busiest_rank": max(0.0, 1.0 - busy_ms_max / ms_fwd) if rig.world > 1 else 0.0,
            "exposed_frac": xs["exposed_frac"] if xs else 0.0,
            "exchange": xs, "parity": par, "gen_s": gen_s, "first_global_rows_rank0": g0s}
     del q, k, v, out, lse
@@ -701,7 +707,7 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
             "k1_probes": {"what": "block kernel alone, ms per launch (rank 0), same shape as one ring step of the headline",
                           "before_any_ring_step": k1_before_ms, "after_timed_region": k1_ms,
                           "interleaved_batches_of_40": {"plain": probe["plain"], "folding_into_partial": probe["merge"],
-                                                        "with_two_d2d_copies_of_a_kv_shard_per_launch": probe["copies"]},
+                                                        "with_two_local_d2d_copies_of_a_kv_shard_per_launch_at_hbm_speed": probe["copies"]},
                           "median_ms": {kk: statistics.median(vv) for kk, vv in probe.items()},
                           "median_sm_mhz": {kk: (statistics.median(vv) if vv else None) for kk, vv in probe_mhz.items()},
                           "median_ms_x_sm_ghz": {kk: (statistics.median(probe[kk]) * statistics.median(vv) / 1e3 if vv else None)
