@@ -77,6 +77,12 @@ def test_merge_and_legacy_entry_reject_bad_arguments(lib):
     assert lib.ring_ctx_create(ctypes.byref(h), 0, 2, None) == _lib.RING_ERR_INVALID_ARGUMENT
     assert lib.ring_ctx_set_option(None, 1, 1) == _lib.RING_ERR_INVALID_ARGUMENT
     assert lib.ring_get_unique_id(None) == _lib.RING_ERR_INVALID_ARGUMENT
+    # the entry points added for tear-down, exchange timings and the no-allocation path's status word
+    assert lib.ring_ctx_abort(None) == _lib.RING_ERR_INVALID_ARGUMENT
+    f = (ctypes.c_float * 2)()
+    assert lib.ring_ctx_get_exchange_timings(None, f, f, 2) == _lib.RING_ERR_INVALID_ARGUMENT
+    assert lib.ring_static_status(None, None) == _lib.RING_ERR_INVALID_ARGUMENT
+    assert b"null" in lib.ring_last_error_string()
 
 
 def test_product_never_imports_the_oracle():
