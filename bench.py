@@ -506,10 +506,10 @@ def run_gpu_arm(args, rank: int, local_rank: int, world: int):
         step_resident()
     ctx.synchronize()
     # Power-steady state: a B200 runs a short burst at 1965 MHz and settles near 1.5 GHz under its 1 kW cap after
-    # some hundred milliseconds of this kernel.  With N GPUs a step is N times longer, so without this phase the
+    # about half a second of this kernel.  With N GPUs a step is N times longer, so without this phase the
     # N = 1 line would be a burst number and the N = 8 line a sustained one.  Untimed; same count on every rank.
     probe_ms = rig.timed(step_resident, 3)[0] / 3
-    n_pre = int(min(2000, max(0, args.prewarm_ms / max(probe_ms, 1e-3))))
+    n_pre = int(min(4000, max(0, args.prewarm_ms / max(probe_ms, 1e-3))))
     for _ in range(n_pre):
         step_resident()
     ctx.synchronize()
@@ -778,7 +778,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--regions", type=int, default=5, help="timed regions of `steps` forwards each; the value is their median")
     ap.add_argument("--e2e-chunks", type=int, default=8, help="(batch, head) groups the host-buffer forward pipelines")
-    ap.add_argument("--prewarm-ms", type=float, default=400.0, help="untimed work before the timed region (power-steady clocks)")
+    ap.add_argument("--prewarm-ms", type=float, default=1500.0,
+                    help="untimed forwards before the timed regions: a B200 needs about half a second of this kernel, from idle, before "
+                         "the 1 kW cap has pulled the clocks down to where they stay (measured: the third 17 ms region after a 400 ms "
+                         "prewarm still ran 13 %% faster than the fifth)")
     ap.add_argument("--transport", default="default", choices=["default", "nccl", "peer"], help="K/V exchange transport")
     ap.add_argument("--merge-mode", type=int, default=None, choices=[0, 1], help="0 separate merge kernel, 1 fused epilogue")
     ap.add_argument("--configs", default="auto", help="auto: the BASELINE.json configurations of this GPU count; none; or a comma list")
