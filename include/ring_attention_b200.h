@@ -56,6 +56,11 @@ struct Ring_fwd_params; /* csrc/ring.h of this repository: the reference's struc
                                            Contiguous causal sharding (the default) makes rank r do (r + 1/2) / npes of the
                                            work; zig-zag gives every rank the same.  Needs equal, even shard lengths. */
 
+#define RING_OPT_RECV_BUFFERS 6         /* receive buffers of the exchange: 2 (default, a double buffer: an exchange waits until
+                                           the compute step that last read its buffer is done) ... world - 1, or 0 = one per
+                                           remote shard (no exchange ever waits for a compute step; (world - 1) x the K/V
+                                           shard in memory).  Collective: every rank must use the same value. */
+
 /* Transports of the K/V exchange.  Both keep the same schedule (ring_step_plan) and the same double buffer.
  *   NCCL:      ncclSend/ncclRecv on the exchange stream (what the reference's NCCL prototype does,
  *              test/ring_attention_with_nccl.cu:153-156).  NCCL's copy kernels occupy SMs next to the block kernel.

@@ -26,6 +26,7 @@ RING_OPT_CAUSAL_SKIP_EXCHANGE = 2
 RING_OPT_RECORD_TIMINGS = 3
 RING_OPT_TRANSPORT = 4
 RING_OPT_CAUSAL_ZIGZAG = 5
+RING_OPT_RECV_BUFFERS = 6
 RING_TRANSPORT_NCCL = 0
 RING_TRANSPORT_PEER_COPY = 1
 RING_STATIC_MAX_ROWS = 65536

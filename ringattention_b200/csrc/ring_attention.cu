@@ -447,9 +447,11 @@ struct RingCtx {
     cudaEvent_t ev_copy_start[kMaxWorld] = {};  // after the exchange's wait for its go-ahead (credit flag / previous compute)
     cudaEvent_t ev_compute_start[kMaxWorld] = {};
     cudaEvent_t ev_compute_done[kMaxWorld] = {};
-    // receive double buffer: recv[i] holds K then V of one shard
-    void* recv[2] = {nullptr, nullptr};
-    size_t recv_cap[2] = {0, 0};  // bytes
+    // receive buffers: recv[i] holds K then V of one shard; two of them (double buffer) unless RING_OPT_RECV_BUFFERS
+    // asks for one per remote shard
+    void* recv[kMaxWorld] = {};
+    size_t recv_cap[kMaxWorld] = {};  // bytes
+    int recv_buffers = 2;             // 0: one per remote shard (world - 1)
     // partial result of one step (separate-kernel merge mode) and an LSE buffer for callers that pass none
     float* o_part = nullptr;
     float* lse_part = nullptr;
@@ -471,6 +473,7 @@ struct RingCtx {
     uint32_t* peer_flags[kMaxWorld] = {};
     void* recv_block = nullptr;       // one allocation holding both receive buffers (peer transport)
     size_t recv_block_half = 0;       // bytes of one receive buffer inside the block
+    int recv_block_count = 0;         // receive buffers inside the block
     void* peer_recv_block[kMaxWorld] = {};
     size_t peer_recv_half[kMaxWorld] = {};
     void* xchg_dev = nullptr;         // staging for the handle all-gathers
@@ -601,14 +604,15 @@ int peer_setup_flags(RingCtx* c) {
 }
 
 // Collective: every rank of the context calls it in the same ring_attention_fwd() with the same size.
-int peer_grow_recv(RingCtx* c, size_t half_bytes) {
-    if (half_bytes <= c->recv_block_half) return RING_OK;
+int peer_grow_recv(RingCtx* c, size_t half_bytes, int nbuf) {
+    if (half_bytes <= c->recv_block_half && nbuf <= c->recv_block_count) return RING_OK;
+    if (half_bytes < c->recv_block_half) half_bytes = c->recv_block_half;
     int rc;
     std::vector<char> all;
     char blob[kXchgBlob] = {0};
     RING_CUDA(cudaDeviceSynchronize());
     if (!c->recv_block) {  // buffers an earlier NCCL-transport forward obtained with grow(): not shared, release them
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < kMaxWorld; ++i) {
             if (c->recv[i]) RING_CUDA(cudaFree(c->recv[i]));
             c->recv[i] = nullptr;
             c->recv_cap[i] = 0;
@@ -622,8 +626,10 @@ int peer_grow_recv(RingCtx* c, size_t half_bytes) {
     if (c->recv_block) RING_CUDA(cudaFree(c->recv_block));
     c->recv_block = nullptr;
     c->recv_block_half = 0;
-    RING_CUDA(cudaMalloc(&c->recv_block, 2 * half_bytes));
+    c->recv_block_count = 0;
+    RING_CUDA(cudaMalloc(&c->recv_block, static_cast<size_t>(nbuf) * half_bytes));
     c->recv_block_half = half_bytes;
+    c->recv_block_count = nbuf;
     HandleBlob mine;
     std::memset(&mine, 0, sizeof(mine));
     RING_CUDA(cudaIpcGetMemHandle(&mine.handle, c->recv_block));
@@ -638,9 +644,10 @@ int peer_grow_recv(RingCtx* c, size_t half_bytes) {
         if (r == c->rank) { c->peer_recv_block[r] = c->recv_block; continue; }
         RING_CUDA(cudaIpcOpenMemHandle(&c->peer_recv_block[r], hb.handle, cudaIpcMemLazyEnablePeerAccess));
     }
-    c->recv[0] = c->recv_block;
-    c->recv[1] = static_cast<char*>(c->recv_block) + half_bytes;
-    c->recv_cap[0] = c->recv_cap[1] = half_bytes;
+    for (int i = 0; i < kMaxWorld; ++i) {
+        c->recv[i] = i < nbuf ? static_cast<char*>(c->recv_block) + static_cast<size_t>(i) * half_bytes : nullptr;
+        c->recv_cap[i] = i < nbuf ? half_bytes : 0;
+    }
     return RING_OK;
 }
 
@@ -733,16 +740,21 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
     }
 
     const bool peer = !c->local && P > 1 && c->transport == RING_TRANSPORT_PEER_COPY;
+    // Receive buffers: exchange e lands in buffer e % nbuf and compute step s >= 1 reads buffer (s - 1) % nbuf.  With two
+    // (the default) exchange e must wait until step e - 1 has read the buffer; with one per remote shard no exchange
+    // ever waits for a compute step.
+    const int nbuf = P > 1 ? ((c->recv_buffers <= 0 || c->recv_buffers > P - 1) ? (P - 1 > 1 ? P - 1 : 1) : c->recv_buffers) : 1;
+    auto compute_buf = [&](int step) { return (step - 1) % nbuf; };
     StreamMemOps ops;
     uint32_t seq = 0;
     if (peer) {
         if ((rc = stream_mem_ops(&ops))) return rc;
-        if ((rc = peer_grow_recv(c, 2 * max_shard_bytes))) return rc;
+        if ((rc = peer_grow_recv(c, 2 * max_shard_bytes, nbuf))) return rc;
         seq = ++c->call_seq;
     } else {
         if (c->recv_block) return fail(RING_ERR_UNSUPPORTED, "switching from the peer-copy transport back to NCCL is not supported");
-        if (P > 1 && (rc = grow(&c->recv[0], &c->recv_cap[0], 2 * max_shard_bytes))) return rc;
-        if (P > 2 && (rc = grow(&c->recv[1], &c->recv_cap[1], 2 * max_shard_bytes))) return rc;
+        for (int i = 0; i < nbuf && i < P - 1; ++i)
+            if ((rc = grow(&c->recv[i], &c->recv_cap[i], 2 * max_shard_bytes))) return rc;
     }
     float* lse = static_cast<float*>(p.lse_ptr);
     if (!lse) {
@@ -762,9 +774,9 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_fork, 0));
     }
     if (peer) {
-        // Both receive buffers are free here (their last readers precede this point on `stream`): tell the
-        // origins of the first two exchanges.
-        for (int e = 0; e < 2 && e < P - 1; ++e) {
+        // Every receive buffer is free here (their last readers precede this point on `stream`): tell the
+        // origins of the first nbuf exchanges.
+        for (int e = 0; e < nbuf && e < P - 1; ++e) {
             RingStepPlan pe;
             if ((rc = ring_step_plan(P, r, e, plan_causal, c->causal_skip, &pe))) return rc;
             if (pe.do_recv)
@@ -790,9 +802,11 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             const bool do_recv = plan.do_recv != 0;
             const bool do_send = plan.do_send != 0;
             if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_comm_start[s], c->comm_stream));
-            if (s >= 2 && !peer) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - 1], 0));
+            // buffer s % nbuf was last read by compute step s - nbuf + 1
+            if (s >= nbuf && !peer) RING_CUDA(cudaStreamWaitEvent(c->comm_stream, c->ev_compute_done[s - nbuf + 1], 0));
             if (c->record_timings && !peer) RING_CUDA(cudaEventRecord(c->ev_copy_start[s], c->comm_stream));
-            char* dst_k = static_cast<char*>(c->recv[plan.recv_buffer]);
+            const int recv_buf = s % nbuf;
+            char* dst_k = static_cast<char*>(c->recv[recv_buf]);
             char* dst_v = dst_k + max_shard_bytes;
             const size_t in_bytes = bytes_of(nsrc);
             if (peer) {
@@ -800,7 +814,7 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
                     CUstream cs = reinterpret_cast<CUstream>(c->comm_stream);
                     RING_CU(ops.wait(cs, reinterpret_cast<CUdeviceptr>(c->flags + kFlagCredit + s), seq, CU_STREAM_WAIT_VALUE_GEQ));
                     if (c->record_timings) RING_CUDA(cudaEventRecord(c->ev_copy_start[s], c->comm_stream));
-                    char* remote = static_cast<char*>(c->peer_recv_block[ndst]) + plan.recv_buffer * c->peer_recv_half[ndst];
+                    char* remote = static_cast<char*>(c->peer_recv_block[ndst]) + static_cast<size_t>(recv_buf) * c->peer_recv_half[ndst];
                     RING_CUDA(cudaMemcpyAsync(remote, p.k_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                     RING_CUDA(cudaMemcpyAsync(remote + max_shard_bytes, p.v_ptr, shard_bytes, cudaMemcpyDeviceToDevice, c->comm_stream));
                     RING_CU(ops.write(cs, reinterpret_cast<CUdeviceptr>(c->peer_flags[ndst] + kFlagReady + s), seq, 0));
@@ -852,9 +866,9 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         if (compute && zig) {
             // four half-shard products per step, of which the causal mask leaves two (three on the own shard)
             const int half = S / 2;
-            const char* kbase = static_cast<const char*>(plan.compute_buffer < 0 ? p.k_ptr : c->recv[plan.compute_buffer]);
-            const char* vbase = plan.compute_buffer < 0 ? static_cast<const char*>(p.v_ptr)
-                                                        : static_cast<const char*>(c->recv[plan.compute_buffer]) + max_shard_bytes;
+            const char* kbase = static_cast<const char*>(s == 0 ? p.k_ptr : c->recv[compute_buf(s)]);
+            const char* vbase = s == 0 ? static_cast<const char*>(p.v_ptr)
+                                       : static_cast<const char*>(c->recv[compute_buf(s)]) + max_shard_bytes;
             for (int qp = 0; qp < 2; ++qp) {
                 for (int kp = 0; kp < 2; ++kp) {
                     const int q_chunk = qp ? 2 * P - 1 - r : r;
@@ -881,8 +895,8 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
         } else if (compute) {
             BlockLaunch L;
             L.q = p.q_ptr;
-            L.k = plan.compute_buffer < 0 ? p.k_ptr : c->recv[plan.compute_buffer];
-            L.v = plan.compute_buffer < 0 ? p.v_ptr : static_cast<char*>(c->recv[plan.compute_buffer]) + max_shard_bytes;
+            L.k = s == 0 ? p.k_ptr : c->recv[compute_buf(s)];
+            L.v = s == 0 ? p.v_ptr : static_cast<char*>(c->recv[compute_buf(s)]) + max_shard_bytes;
             L.batch = B;
             L.heads = H;
             L.sq = S;
@@ -909,13 +923,14 @@ int run_ring_fwd(RingCtx* c, const Ring_fwd_params& p, cudaStream_t stream) {
             have_partial = true;
         }
         RING_CUDA(cudaEventRecord(c->ev_compute_done[s], stream));
-        if (peer && s >= 1 && s + 1 <= P - 2) {
-            // step s was the last reader of receive buffer (s - 1) & 1 = (s + 1) & 1: free it for exchange s + 1
+        if (peer && s >= 1 && s - 1 + nbuf <= P - 2) {
+            // step s was the last reader of receive buffer (s - 1) % nbuf: free it for exchange s - 1 + nbuf
+            const int e = s - 1 + nbuf;
             RingStepPlan pe;
-            if ((rc = ring_step_plan(P, r, s + 1, plan_causal, c->causal_skip, &pe))) return rc;
+            if ((rc = ring_step_plan(P, r, e, plan_causal, c->causal_skip, &pe))) return rc;
             if (pe.do_recv)
                 RING_CU(ops.write(reinterpret_cast<CUstream>(stream),
-                                  reinterpret_cast<CUdeviceptr>(c->peer_flags[pe.recv_from] + kFlagCredit + s + 1), seq, 0));
+                                  reinterpret_cast<CUdeviceptr>(c->peer_flags[pe.recv_from] + kFlagCredit + e), seq, 0));
         }
     }
     if (peer) {
@@ -1119,6 +1134,10 @@ int ring_ctx_set_option(RingCtx* ctx, int option, int value) {
         case RING_OPT_CAUSAL_ZIGZAG:
             ctx->zigzag = value ? 1 : 0;
             return RING_OK;
+        case RING_OPT_RECV_BUFFERS:
+            if (value < 0 || value == 1 || value > kMaxWorld) return fail(RING_ERR_INVALID_ARGUMENT, "bad receive-buffer count %d", value);
+            ctx->recv_buffers = value;
+            return RING_OK;
         case RING_OPT_TRANSPORT:
             if (value != RING_TRANSPORT_NCCL && value != RING_TRANSPORT_PEER_COPY)
                 return fail(RING_ERR_INVALID_ARGUMENT, "bad transport %d", value);
@@ -1139,6 +1158,7 @@ int ring_ctx_get_option(RingCtx* ctx, int option, int* value) {
         case RING_OPT_RECORD_TIMINGS: *value = ctx->record_timings; return RING_OK;
         case RING_OPT_TRANSPORT: *value = ctx->transport; return RING_OK;
         case RING_OPT_CAUSAL_ZIGZAG: *value = ctx->zigzag; return RING_OK;
+        case RING_OPT_RECV_BUFFERS: *value = ctx->recv_buffers; return RING_OK;
         default: return fail(RING_ERR_INVALID_ARGUMENT, "unknown option %d", option);
     }
 }
@@ -1175,7 +1195,10 @@ int ring_ctx_destroy(RingCtx* c) {
         if (c->peer_recv_block[i]) cudaIpcCloseMemHandle(c->peer_recv_block[i]);
         if (c->peer_flags[i]) cudaIpcCloseMemHandle(c->peer_flags[i]);
     }
-    if (c->recv_block) { cudaFree(c->recv_block); c->recv[0] = c->recv[1] = nullptr; }
+    if (c->recv_block) {
+        cudaFree(c->recv_block);
+        for (int i = 0; i < kMaxWorld; ++i) c->recv[i] = nullptr;
+    }
     if (c->flags) cudaFree(c->flags);
     if (c->xchg_dev) cudaFree(c->xchg_dev);
     for (int i = 0; i < 2; ++i) {
@@ -1191,7 +1214,7 @@ int ring_ctx_destroy(RingCtx* c) {
     if (c->ev_call_done) cudaEventDestroy(c->ev_call_done);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->comm_stream) cudaStreamDestroy(c->comm_stream);
-    for (int i = 0; i < 2; ++i)
+    for (int i = 0; i < kMaxWorld; ++i)
         if (c->recv[i]) cudaFree(c->recv[i]);
     if (c->o_part) cudaFree(c->o_part);
     if (c->lse_part) cudaFree(c->lse_part);

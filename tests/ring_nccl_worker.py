@@ -39,6 +39,7 @@ def main():
     ap.add_argument("--merge-mode", type=int, default=1)
     ap.add_argument("--out", default="")
     ap.add_argument("--transport", default="default", choices=["default", "nccl", "peer"])
+    ap.add_argument("--recv-buffers", type=int, default=2)
     args = ap.parse_args()
 
     import torch
@@ -65,6 +66,7 @@ def main():
         ctx.set_option(ra.RING_OPT_TRANSPORT, ra.RING_TRANSPORT_NCCL if args.transport == "nccl" else ra.RING_TRANSPORT_PEER_COPY)
     transport = "peer" if ctx.get_option(ra.RING_OPT_TRANSPORT) == ra.RING_TRANSPORT_PEER_COPY else "nccl"
     ctx.set_option(ra.RING_OPT_MERGE_MODE, args.merge_mode)
+    ctx.set_option(ra.RING_OPT_RECV_BUFFERS, args.recv_buffers)
     ctx.set_option(ra.RING_OPT_RECORD_TIMINGS, 1)
     ctx.set_option(ra.RING_OPT_CAUSAL_ZIGZAG, int(bool(cfg.get("zigzag"))))
     for _ in range(3):

@@ -19,7 +19,7 @@ def rows_per_cta(request, monkeypatch):
         monkeypatch.setenv("RING_ROWS_PER_CTA", request.param)
 
 
-def _ring_local(ra, q, k, v, world, scale, causal, merge_mode, poison=True):
+def _ring_local(ra, q, k, v, world, scale, causal, merge_mode, poison=True, recv_buffers=None):
     import torch
     B, H, S, D = q.shape
     Sl = S // world
@@ -28,6 +28,9 @@ def _ring_local(ra, q, k, v, world, scale, causal, merge_mode, poison=True):
     ctx = ra.RingContext.create_local(world)
     ctx.set_option(ra.RING_OPT_MERGE_MODE, merge_mode)
     ctx.set_option(ra.RING_OPT_RECORD_TIMINGS, 1)
+    if recv_buffers is not None:
+        ctx.set_option(ra.RING_OPT_RECV_BUFFERS, recv_buffers)
+        assert ctx.get_option(ra.RING_OPT_RECV_BUFFERS) == recv_buffers
     ctx.set_local_shards(ks, vs)
     outs, lses = [], []
     for r in range(world):
@@ -62,6 +65,19 @@ def test_virtual_ring_matches_oracle(ra, world, causal, merge_mode):
     # and the blocked restatement of the reference's device algorithm agrees as well
     ring_o, ring_lse = oracle.ring_attention_fwd(q, k, v, world, scale, causal, block_n=128, round_p=True)
     assert_parity(o, lse, ring_o, ring_lse, "ring vs blocked oracle")
+
+
+@pytest.mark.parametrize("recv_buffers", [0, 3], ids=["one-per-shard", "three"])
+@pytest.mark.parametrize("world,causal", [(4, False), (8, True), (5, False)])
+def test_virtual_ring_more_receive_buffers(ra, world, causal, recv_buffers):
+    """RING_OPT_RECV_BUFFERS: one receive buffer per remote shard (no exchange waits for a compute step) or three."""
+    B, H, D = 1, 2, 128
+    S = 256 * world
+    q, k, v = synthetic.make_qkv(1100 + world, B, H, D, 0, S)
+    scale = D ** -0.5
+    o, lse = _ring_local(ra, q, k, v, world, scale, causal, 1, recv_buffers=recv_buffers)
+    want_o, want_lse = oracle.attention_fwd(q, k, v, scale, causal)
+    assert_parity(o, lse, want_o, want_lse, f"ring world={world} recv_buffers={recv_buffers}")
 
 
 def test_virtual_ring_d64_three_ranks(ra):

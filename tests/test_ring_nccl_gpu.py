@@ -23,13 +23,13 @@ def _free_port():
     return p
 
 
-def _run(world, config, merge_mode, tmp_path, timeout=1500, transport="default"):
+def _run(world, config, merge_mode, tmp_path, timeout=1500, transport="default", recv_buffers=2):
     out = os.path.join(str(tmp_path), f"{config}_{merge_mode}_{transport}.json")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "ring_nccl_worker.py"), "--config", config, "--merge-mode", str(merge_mode), "--out", out,
-           "--transport", transport]
+           "--transport", transport, "--recv-buffers", str(recv_buffers)]
     res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     r = json.load(open(out))
@@ -133,3 +133,14 @@ def test_peer_stops_rank_aborts_and_leaves(tmp_path):
     assert r0["refused_after_abort"] is True
     assert r0["destroy_s"] <= 8.0
     assert r0["device_status"] == 0 and by_rank[1]["device_status"] == 0
+
+
+@pytest.mark.parametrize("world", [4, 8])
+@pytest.mark.parametrize("transport", ["nccl", "peer"])
+@pytest.mark.parametrize("config", ["small", "uneven_causal"])
+def test_ring_one_receive_buffer_per_shard(world, config, transport, tmp_path):
+    """RING_OPT_RECV_BUFFERS = 0 on real ranks: every exchange has a buffer of its own, none waits for a compute step."""
+    if _gpus() < world:
+        pytest.skip(f"needs {world} GPUs")
+    r = _run(world, config, 1, tmp_path, transport=transport, recv_buffers=0)
+    assert r["transport"] == transport
