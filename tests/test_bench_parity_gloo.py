@@ -1,7 +1,7 @@
 """The multi-rank parity check that bench.py and the multi-GPU worker print (`parity` objects), run on CPU ranks
 (gloo, world 2): every rank builds its shard with bench.make_rank_inputs -- contiguous, uneven and zig-zag shardings,
 fp16 and bf16 -- fills its "output" with the oracle's full attention of its own rows, and bench.check_parity must
-accept it; one wrong row on ONE rank, or rows left unwritten, must fail the check on EVERY rank (the verdict is
+accept it; one wrong row on ONE rank, or rows left unwritten, must fail the check on EVERY rank (the result is
 max-reduced), which is what makes a stale or misplaced K/V shard visible in the benchmark's line."""
 import os
 import socket
@@ -96,7 +96,7 @@ def test_parity_check_on_gloo_ranks(tmp_path):
             assert got["bad"] is False and got["bad_err"] >= 5e-3, (name, r, got)      # rank 1's wrong row fails rank 0 too
             assert got["unwritten"] is False and got["unwritten_flag"] is True, (name, r, got)
             assert got["rows"] >= 2 * 20
-        assert per_rank[0][name] == per_rank[1][name]                                  # every rank reports the reduced verdict
+        assert per_rank[0][name] == per_rank[1][name]                                  # every rank reports the reduced result
 
 
 def test_bench_config_table_is_consistent():
