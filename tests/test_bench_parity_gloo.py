@@ -112,3 +112,24 @@ def test_bench_config_table_is_consistent():
     assert bench.config_flops(bench.CONFIGS["c1"]) == 4.0 * 64 * 8 * 1024 * 1024
     c4 = bench.CONFIGS["c4"]
     assert bench.config_flops(c4) == 4.0 * 128 * 32 * (131072 * 131073 / 2)
+
+
+def test_reference_arm_under_a_two_process_launcher():
+    """`bench.py --impl reference` launched like the multi-GPU arm (torchrun, two processes, which exports
+    OMP_NUM_THREADS=1): rank 0 alone prints the line, it uses every host core all the same, labels the workload of
+    that GPU count, and carries the same `config` object as the GPU arm would."""
+    import json
+    import subprocess
+    import bench
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(_free_port()), os.path.join(ROOT, "bench.py"), "--impl", "reference", "--gpus", "2",
+           "--steps", "1", "--warmup", "0"]
+    res = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, lines                       # the other rank exits without a line
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["n_gpus"] == 2 and d["gpu_launches"] == 0
+    assert d["config"] == bench.workload_config(2) and "total seq 16384" in d["config"]["workload"]
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] == (os.cpu_count() or 1)
+    assert d["e2e"]["value"] == d["value"] > 0 and d["e2e"]["h2d_bytes_per_step"] == 0
