@@ -41,6 +41,9 @@ def _ring_local(ra, q, k, v, world, scale, causal, merge_mode, poison=True, recv
     ctx.synchronize()
     t = ctx.timings()
     assert len(t[0]) == world and all(x >= 0 for x in t[0])
+    wait_ms, copy_ms = ctx.exchange_timings()   # the exchange of every step, split into its wait and its copy
+    assert len(wait_ms) == world and all(x >= 0 for x in wait_ms) and all(x >= 0 for x in copy_ms)
+    assert copy_ms[world - 1] == 0 and (world == 1 or sum(copy_ms) > 0 or causal)
     ctx.destroy()
     return torch.cat(outs, 2).cpu().numpy(), torch.cat(lses, 2).cpu().numpy()
 
