@@ -365,6 +365,13 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
                     for (int u = 0; u < 4; u += 2) {
                         float x0, x1;
                         ffma2(x0, x1, s[i + u], s[i + u + 1], c, c, nms, nms);
+                        // At head dimension 64 the kernel is bound by the MUFU (the tensor pipe has half the work per
+                        // exponential): one pair in four is evaluated on the FMA pipe instead.  At 128 that costs more
+                        // than it saves (measured both ways).
+                        if (D == 64 && ((i + u) / 2) % 4 == 3) {
+                            ex2_poly2(s[i + u], s[i + u + 1], x0, x1);
+                            continue;
+                        }
                         s[i + u] = ex2_approx(x0);
                         s[i + u + 1] = ex2_approx(x1);
                     }

@@ -438,6 +438,35 @@ __device__ __forceinline__ float ex2_approx(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ void fsub2(float& d0, float& d1, float a0, float a1, float b0, float b1) {
+    asm("{\n\t"
+        ".reg .b64 ra, rb, rd;\n\t"
+        "mov.b64 ra, {%2, %3};\n\t"
+        "mov.b64 rb, {%4, %5};\n\t"
+        "sub.rn.f32x2 rd, ra, rb;\n\t"
+        "mov.b64 {%0, %1}, rd;\n\t"
+        "}"
+        : "=f"(d0), "=f"(d1)
+        : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// 2^x for a pair of values on the FMA pipe instead of the MUFU: n = round(x) by the magic-number add, 2^(x - n) by a
+// degree-4 minimax polynomial on [-0.5, 0.5] (relative error < 3e-6), n added into the exponent field.
+// x is clamped below at -126 (the result, 2^-126, is zero for every purpose here) and must be below 127.
+__device__ __forceinline__ void ex2_poly2(float& y0, float& y1, float x0, float x1) {
+    const float kMagic = 12582912.f;  // 1.5 * 2^23
+    x0 = fmaxf(x0, -126.f);
+    x1 = fmaxf(x1, -126.f);
+    float r0, r1, n0, n1, f0, f1, p0, p1;
+    fadd2(r0, r1, x0, x1, kMagic, kMagic);
+    fsub2(n0, n1, r0, r1, kMagic, kMagic);
+    fsub2(f0, f1, x0, x1, n0, n1);
+    ffma2(p0, p1, f0, f1, 9.570101276e-03f, 9.570101276e-03f, 5.591785908e-02f, 5.591785908e-02f);
+    ffma2(p0, p1, p0, p1, f0, f1, 2.402474433e-01f, 2.402474433e-01f);
+    ffma2(p0, p1, p0, p1, f0, f1, 6.931217909e-01f, 6.931217909e-01f);
+    ffma2(p0, p1, p0, p1, f0, f1, 9.999992847e-01f, 9.999992847e-01f);
+    y0 = __int_as_float(__float_as_int(p0) + (__float_as_int(r0) << 23));
+    y1 = __int_as_float(__float_as_int(p1) + (__float_as_int(r1) << 23));
+}
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
