@@ -12,8 +12,9 @@
 //     tile per CTA when the two-tile grid would leave more than half of the SMs idle, args.rows_per_cta);
 //   * one thread issues TMA loads (Q once, then K_j and V_j through two rings of shared-memory slots,
 //     128-byte swizzle, 64-element boxes);
-//   * three threads of three warps issue tcgen05.mma, because one thread sustains only about one 128x128x16
-//     instruction per 100 clocks while the pipe takes one per ~70.  The first issues S_t = Q_t K_j^T for both
+//   * three threads of three warps issue tcgen05.mma, because inside this kernel one thread gets only about one
+//     128x128x16 instruction out per 100-115 clocks (its warp shares a scheduler with two softmax warps; alone on
+//     an SM the same thread issues one per ~76, the pipe's own rate at M = 128).  The first issues S_t = Q_t K_j^T for both
 //     tiles (both operands K-major in shared memory, N = 128: a narrower N would re-read Q from shared memory,
 //     whose ~75 B/clock operand bandwidth is what bounds these instructions) into ONE S buffer of 128 TMEM
 //     columns that the two Q tiles use in turn; the other two issue O_t += P_t V_j for tile 0 / 1, reading P_t
@@ -218,8 +219,8 @@ ring_block_attention_kernel(const __grid_constant__ CUtensorMap tm_q, const __gr
             __syncwarp();
         } else if (warp == T::kMmaWarp) {
             // =================================================================== UMMA issuer: S = Q K^T, both tiles
-            // (One thread sustains roughly one tcgen05.mma per 110 clocks, so the three MMA streams of the CTA
-            //  -- S for both tiles, P V for tile 0, P V for tile 1 -- are issued by three different warps.)
+            // (Next to the softmax warps one thread gets roughly one tcgen05.mma out per 110 clocks, so the three MMA
+            //  streams of the CTA -- S for both tiles, P V for tile 0, P V for tile 1 -- are issued by three warps.)
             if (lane == 0 && nblk > 0) {
                 // S = Q_t K^T into the shared S buffer: D/16 instructions of 128 x 128 x 16
                 auto issue_qk = [&](int t, int kslot) {
